@@ -1,0 +1,220 @@
+"""Python face of the CUDA kernels: argument checks, then one ctypes call per launch.
+
+Every function works on torch CUDA tensors, launches on torch's current stream (so a
+launch can be captured in a CUDA graph) and returns nothing; outputs are written into
+tensors the caller passes.  Sizes a kernel does not take are refused with UnsupportedShape
+before anything runs.  There is no other implementation behind these functions: if the
+library cannot be built or loaded, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+ACT_CODES = {None: 0, "none": 0, "gelu_new": 1, "gelu_tanh": 1, "gelu": 2, "gelu_erf": 2}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class UnsupportedShape(KernelError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise UnsupportedShape(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise UnsupportedShape(f"{what}: sizes or dtypes not supported by this kernel")
+    if code == -2:
+        raise KernelError(f"{what}: bad argument (null pointer or impossible size)")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must be CUDA tensors (there is no CPU path)")
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+# --------------------------------------------------------------------------------------
+def embed_positions(ids, positions, wte, wpe, out, status=None) -> None:
+    """out[t] = wte[ids[t]] + wpe[positions[t]] (wpe may be None)."""
+    _cuda(ids, positions, wte, wpe, out)
+    _i32(ids, "ids")
+    n, width = out.shape
+    if wpe is not None:
+        _i32(positions, "positions")
+        if wpe.dtype != wte.dtype or wpe.shape[1] != width:
+            raise KernelError("position table must match the token table in dtype and width")
+    if wte.shape[1] != width or not (wte.is_contiguous() and out.is_contiguous()):
+        raise KernelError("embed_positions: tables and output must be contiguous and of one width")
+    lib = load_library("embed")
+    code = lib.sandy_embed_pos(_p(ids), _p(positions), _p(wte), _p(wpe), _p(out),
+                               ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(wte.shape[0]),
+                               ctypes.c_int(0 if wpe is None else wpe.shape[0]),
+                               ctypes.c_int(_dt(wte)), ctypes.c_int(_dt(out)), _p(status), _stream())
+    _check(code, "embed_positions")
+
+
+def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
+    """out[r] = LayerNorm(x[rows[r]] if rows is given else x[r])."""
+    _cuda(x, gamma, beta, out, rows)
+    width = x.shape[-1]
+    n_rows = out.shape[0]
+    if rows is not None:
+        _i32(rows, "rows")
+        if rows.numel() != n_rows:
+            raise KernelError("layernorm: rows and out disagree")
+    elif x.shape[0] != n_rows:
+        raise KernelError("layernorm: x and out disagree")
+    if not (x.is_contiguous() and out.is_contiguous()) or out.shape[-1] != width or gamma.numel() != width:
+        raise KernelError("layernorm: contiguous [rows, width] tensors expected")
+    lib = load_library("norm")
+    code = lib.sandy_layernorm(_p(x), _p(gamma), _p(beta), _p(out), _p(rows), ctypes.c_int(n_rows),
+                               ctypes.c_int(width), ctypes.c_float(eps), ctypes.c_int(_dt(x)),
+                               ctypes.c_int(_dt(gamma)), ctypes.c_int(_dt(out)), _stream())
+    _check(code, f"layernorm(width={width})")
+
+
+def gemm_simt(a, w, bias, out, *, w_out_in: bool, act=None, residual=None) -> None:
+    """out = act(a @ W + bias) + residual on the 32-bit pipes.  W is [K,N], or [N,K] with w_out_in."""
+    _cuda(a, w, bias, out, residual)
+    M, K = a.shape
+    N = out.shape[1]
+    wk, wn = (w.shape[1], w.shape[0]) if w_out_in else (w.shape[0], w.shape[1])
+    if wk != K or wn != N or out.shape[0] != M:
+        raise KernelError(f"gemm: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)} "
+                          f"({'out_in' if w_out_in else 'in_out'}), out {tuple(out.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm: innermost stride must be 1")
+    if residual is not None and (residual.dtype != torch.float32 or residual.stride(1) != 1
+                                 or tuple(residual.shape) != (M, N)):
+        raise KernelError("gemm: residual must be float32 [M, N]")
+    if bias is not None and (bias.dtype != w.dtype or bias.numel() != N):
+        raise KernelError("gemm: bias must have the weight's dtype and N elements")
+    lib = load_library("gemm_simt")
+    code = lib.sandy_gemm_simt(_p(a), _p(w), _p(bias), _p(residual), _p(out),
+                               ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+                               ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
+                               ctypes.c_int(0 if residual is None else residual.stride(0)),
+                               ctypes.c_int(out.stride(0)), ctypes.c_int(1 if w_out_in else 0),
+                               ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(a)), ctypes.c_int(_dt(w)),
+                               ctypes.c_int(_dt(out)), _stream())
+    _check(code, f"gemm_simt(M={M},N={N},K={K},{a.dtype}->{out.dtype})")
+
+
+def _cache_args(k_cache, v_cache):
+    """k_cache, v_cache: [num_pages, Hkv, page_size, D] views with one page stride."""
+    if k_cache.shape != v_cache.shape or k_cache.dtype != v_cache.dtype or k_cache.dim() != 4:
+        raise KernelError("cache views must be [num_pages, Hkv, page_size, D], K and V alike")
+    _, hkv, ps, d = k_cache.shape
+    want = (k_cache.stride(0), ps * d, d, 1)
+    if tuple(k_cache.stride()) != want or tuple(v_cache.stride()) != want:
+        raise KernelError("cache views must be dense inside a page")
+    return hkv, ps, d, k_cache.stride(0)
+
+
+def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions) -> None:
+    """Write the step's keys/values ([T, Hkv*D] views, one row stride) into their pages."""
+    _cuda(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
+    hkv, ps, d, page_stride = _cache_args(k_cache, v_cache)
+    T = k_src.shape[0]
+    if k_src.shape != v_src.shape or k_src.shape[1] != hkv * d or k_src.stride() != v_src.stride() \
+            or k_src.stride(1) != 1 or k_src.dtype != k_cache.dtype:
+        raise KernelError("kv_append: sources must be [T, Hkv*D] of the cache's dtype with one stride")
+    _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
+    lib = load_library("attention")
+    code = lib.sandy_kv_append(_p(k_src), _p(v_src), ctypes.c_int(k_src.stride(0)), _p(k_cache), _p(v_cache),
+                               ctypes.c_longlong(page_stride), _p(block_table), ctypes.c_int(block_table.shape[1]),
+                               _p(token_seq), _p(positions), ctypes.c_int(T), ctypes.c_int(hkv), ctypes.c_int(d),
+                               ctypes.c_int(ps), ctypes.c_int(_dt(k_cache)), _stream())
+    _check(code, "kv_append")
+
+
+def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *,
+                    n_heads: int, scale: float, window: int = 0) -> None:
+    """Causal attention of every token of the step over its request's pages (general kernel)."""
+    _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
+    hkv, ps, d, page_stride = _cache_args(k_cache, v_cache)
+    T = q.shape[0]
+    if d % 16 != 0 or d > 256:
+        raise UnsupportedShape(f"attention: head size {d} must be a multiple of 16, at most 256")
+    if n_heads % hkv != 0:
+        raise UnsupportedShape(f"attention: {n_heads} heads do not divide into {hkv} key/value heads")
+    if q.shape[1] != n_heads * d or out.shape != q.shape or q.stride(1) != 1 or out.stride(1) != 1 \
+            or q.dtype != k_cache.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
+    _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
+    lib = load_library("attention")
+    code = lib.sandy_paged_attention(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+                                     ctypes.c_longlong(page_stride), _p(block_table),
+                                     ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
+                                     ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads),
+                                     ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale),
+                                     ctypes.c_int(window), ctypes.c_int(_dt(q)), _stream())
+    _check(code, f"paged_attention(H={n_heads},Hkv={hkv},D={d})")
+
+
+def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale: float, window: int = 0) -> None:
+    """Attention of a step's tokens over the cache: picks the kernel for the step's shape."""
+    paged_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out,
+                    n_heads=n_heads, scale=scale, window=window)
+
+
+def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, uniform=None, status=None) -> None:
+    """Choose one token per row of float32 `logits`; per-row option tensors may be None."""
+    _cuda(logits, out_tokens, temperature, top_k, top_p, uniform, status)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 with unit inner stride")
+    n, vocab = logits.shape
+    _i32(out_tokens, "out_tokens")
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("uniform", uniform, torch.float32)):
+        if t is not None and (t.dtype != dt or t.numel() != n or not t.is_contiguous()):
+            raise KernelError(f"sample: {name} must be a contiguous {dt} tensor of one value per row")
+    if temperature is not None and uniform is None:
+        raise KernelError("sample: temperature sampling needs a uniform number per row")
+    lib = load_library("sampling")
+    code = lib.sandy_sample(_p(logits), ctypes.c_int(logits.stride(0)), ctypes.c_int(n), ctypes.c_int(vocab),
+                            _p(temperature), _p(top_k), _p(top_p), _p(uniform), _p(out_tokens), _p(status),
+                            _stream())
+    _check(code, "sample")
+
+
+# --------------------------------------------------------------------------------------
+def tensor_core_gemm_supported(K: int, N: int) -> bool:
+    """Whether the tcgen05 kernel takes a [*, K] x [N, K] product (its operand rows must
+    start on 16-byte boundaries for TMA, so K must be a multiple of 8)."""
+    return False
+
+
+def gemm_tc(a, w, bias, out, *, act=None, residual=None) -> None:
+    raise KernelError("tensor-core gemm is not available")
