@@ -43,7 +43,13 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# Number of kernel launches issued through this module (benchmarks report it).
+LAUNCHES = 0
+
+
 def _check(code: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if code == 0:
         return
     if code == -1:

@@ -1,0 +1,201 @@
+"""LLM: the Python entry point.  Model folder in, generated token ids out.
+
+    llm = LLM("path/to/model", dtype="bfloat16")
+    results = llm.generate([[15496, 11, 616, 1438, 318]], max_tokens=32)
+    results[0].output_ids, results[0].finish_reason
+
+The call mirrors the reference's Model::generate(requestId, inputIds, maxTokens,
+stopTokenIds, samplingOverrides, control, onToken) -> GenerateResult
+(src/server/Model.h:34-48) and its GenerateResult fields (src/server/Session.h:25-34):
+output ids, finish reason, prompt and completion token counts, prefill and decode times
+and rates.  Unlike the reference, which serves one request at a time behind a gate, all
+requests given to `generate` (or added with `add_request`) run together under the scheduler.
+
+Tokens go in and come out as host integers; every step copies its inputs to the device and
+reads the drawn tokens back.
+"""
+from __future__ import annotations
+
+import dataclasses
+import sys
+import time
+from typing import Callable, Dict, Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..models.model import Model, load_model
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler, fresh_seed
+from .scheduler import Request, RequestRefused, RequestState, Scheduler, StepPlan
+from .step import Engine, StepEntry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+@dataclasses.dataclass
+class GenerateResult:
+    """Fields of the reference's GenerateResult (src/server/Session.h:25-34)."""
+    output_ids: List[int]
+    finish_reason: str
+    prompt_tokens: int
+    completion_tokens: int
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    prefill_tokens_per_second: float = 0.0
+    decode_tokens_per_second: float = 0.0
+    preemptions: int = 0
+
+
+def _rate(tokens: int, ms: float) -> float:
+    return tokens / (ms / 1000.0) if ms > 0 else 0.0
+
+
+class LLM:
+    def __init__(self, model: Union[str, Model], *, dtype: str = "bfloat16", device: str = "cuda:0",
+                 cache_tokens: Optional[int] = None, page_size: int = 16, max_live: int = 64,
+                 max_step_tokens: int = 2048, prefill_chunk_tokens: int = 2048,
+                 eos_token_ids: Optional[Sequence[int]] = None, max_context_tokens: int = 0,
+                 use_cuda_graphs: bool = True):
+        """cache_tokens: how many tokens the cache pool holds (default: room for `max_live`
+        requests of full length, capped at 1M tokens).  eos_token_ids: stop tokens added to
+        every request (default: the config's eos_token_id is NOT added; pass it to stop there).
+        max_context_tokens: if > 0, a lower limit on a request's length than the model's."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("sandyrt_b200 needs a CUDA device; there is no CPU path")
+        if isinstance(model, Model):
+            self.model = model
+        else:
+            self.model = load_model(model, device=device, dtype=_DTYPES[dtype])
+        limit = self.model.max_positions
+        if max_context_tokens and max_context_tokens > 0:
+            limit = min(limit, max_context_tokens) if limit else max_context_tokens
+        self.max_positions = limit
+        if cache_tokens is None:
+            cache_tokens = min(max_live * (limit or 4096), 1 << 20)
+        self.engine = Engine(self.model, max_tokens=cache_tokens, page_size=page_size, max_requests=max_live,
+                             use_cuda_graphs=use_cuda_graphs)
+        self.scheduler = Scheduler(self.engine.cache.alloc, max_step_tokens=max_step_tokens,
+                                   prefill_chunk=prefill_chunk_tokens, max_live=max_live,
+                                   max_positions=limit)
+        self.sampler = Sampler(self.model.device)
+        self.eos_token_ids = frozenset(int(t) for t in (eos_token_ids or ()))
+        self._requests: Dict[Hashable, Request] = {}
+        self._seeds: Dict[Hashable, int] = {}
+        self._next_id = 0
+        self._token_host = torch.empty(max(max_live, 1), dtype=torch.int32, pin_memory=True)
+
+    # ---- request interface ----------------------------------------------------------------
+    def add_request(self, prompt_ids: Sequence[int], *, max_tokens: int = 16,
+                    sampling: Optional[SamplingParams] = None, stop_token_ids: Sequence[int] = (),
+                    request_id: Optional[Hashable] = None) -> Hashable:
+        sampling = (sampling or SamplingParams()).validate()
+        rid = request_id if request_id is not None else f"req-{self._next_id}"
+        self._next_id += 1
+        if rid in self._requests:
+            raise RequestRefused(f"request id {rid!r} is in use")
+        vocab = self.model.spec.vocab_size
+        prompt = [int(t) for t in prompt_ids]
+        for t in prompt:
+            if not (0 <= t < vocab):
+                raise RequestRefused(f"token id {t} is outside the vocabulary of {vocab}")
+        req = Request(rid, prompt, int(max_tokens), frozenset(int(s) for s in stop_token_ids) | self.eos_token_ids,
+                      sampling)
+        req.t_added = time.perf_counter()
+        self.scheduler.add(req)
+        self._requests[rid] = req
+        self._seeds[rid] = sampling.seed if sampling.seed is not None else fresh_seed()
+        return rid
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> List[Request]:
+        """Plan and run one step.  Returns the requests that received a token in it."""
+        plan = self.scheduler.plan()
+        if not plan.portions:
+            return []
+        now = time.perf_counter()
+        entries, sampled_reqs = [], []
+        for p in plan.portions:
+            req = p.request
+            if req.t_first_scheduled == 0.0:
+                req.t_first_scheduled = now
+            toks = req.tokens[p.start:p.start + p.count]
+            entries.append(StepEntry(req.rid, toks, [p.count - 1] if p.samples else []))
+            if p.samples:
+                sampled_reqs.append(req)
+        logits = self.engine.step(entries, reserved=True)
+        sampled: Dict[Hashable, int] = {}
+        if sampled_reqs:
+            n = len(sampled_reqs)
+            tokens = self.sampler.sample(
+                logits, [r.sampling for r in sampled_reqs], [self._seeds[r.rid] for r in sampled_reqs],
+                [len(r.output) for r in sampled_reqs])
+            if self._token_host.numel() < n:
+                self._token_host = torch.empty(n, dtype=torch.int32, pin_memory=True)
+            self._token_host[:n].copy_(tokens, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            host = self._token_host[:n].tolist()
+            if any(t < 0 for t in host):
+                self.sampler.check_status()
+            sampled = {r.rid: t for r, t in zip(sampled_reqs, host)}
+        now = time.perf_counter()
+        for r in sampled_reqs:
+            if r.t_first_token == 0.0:
+                r.t_first_token = now
+        for r in self.scheduler.complete(plan, sampled):
+            r.t_finished = now
+        return sampled_reqs
+
+    def result(self, rid: Hashable) -> GenerateResult:
+        r = self._requests[rid]
+        t_end = r.t_finished or time.perf_counter()
+        prefill_ms = max(0.0, ((r.t_first_token or t_end) - (r.t_first_scheduled or r.t_added)) * 1e3)
+        decode_ms = max(0.0, (t_end - (r.t_first_token or t_end)) * 1e3)
+        n_out = len(r.output)
+        return GenerateResult(list(r.output), r.finish_reason or "", len(r.prompt), n_out, prefill_ms, decode_ms,
+                              _rate(len(r.prompt), prefill_ms), _rate(max(n_out - 1, 0), decode_ms), r.preemptions)
+
+    def forget(self, rid: Hashable) -> None:
+        self._requests.pop(rid, None)
+        self._seeds.pop(rid, None)
+
+    def abort(self, rid: Hashable) -> None:
+        self.scheduler.abort(rid, "cancelled")
+
+    # ---- the blocking convenience -----------------------------------------------------------
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], *, max_tokens: int = 16,
+                 temperature: float = 0.0, top_p: float = 1.0, top_k: int = 0, seed: Optional[int] = None,
+                 stop_token_ids: Sequence[int] = (),
+                 on_token: Optional[Callable[[Hashable, int], bool]] = None,
+                 report: bool = False) -> List[GenerateResult]:
+        """Generate for one prompt (a list of ids) or several (a list of lists).  `on_token`
+        is called with (request index, token) for every new token; returning False cancels
+        that request (finish reason "cancelled"; the reference fails the request with
+        "request cancelled", src/server/Session.cpp:491-492)."""
+        single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
+        batch = [prompts] if single else list(prompts)
+        rids = []
+        for i, p in enumerate(batch):
+            s = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p,
+                               seed=None if seed is None else seed + i)
+            rids.append(self.add_request(p, max_tokens=max_tokens, sampling=s, stop_token_ids=stop_token_ids))
+        index = {rid: i for i, rid in enumerate(rids)}
+        while any(self._requests[r].state is not RequestState.FINISHED for r in rids):
+            got = self.step()
+            if on_token:
+                for r in got:
+                    if r.rid in index and on_token(index[r.rid], r.output[-1]) is False \
+                            and r.state is not RequestState.FINISHED:
+                        self.abort(r.rid)
+        results = [self.result(r) for r in rids]
+        for r in rids:
+            self.forget(r)
+        if report:
+            for res in results:
+                # the reference prints the same line to stderr (src/server/Session.cpp:539-548)
+                print(f"sandy throughput: prefill_tokens={res.prompt_tokens} prefill_ms={res.prefill_ms:.3f} "
+                      f"prefill_toks_per_s={res.prefill_tokens_per_second:.3f} "
+                      f"decode_tokens={res.completion_tokens} decode_ms={res.decode_ms:.3f} "
+                      f"decode_toks_per_s={res.decode_tokens_per_second:.3f}", file=sys.stderr)
+        return results

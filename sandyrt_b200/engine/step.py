@@ -76,7 +76,8 @@ class _Staging:
 class Engine:
     """A bound model, its cache and the step function over them."""
 
-    def __init__(self, model: Model, *, max_tokens: int, page_size: int = 16, max_requests: int = 64):
+    def __init__(self, model: Model, *, max_tokens: int, page_size: int = 16, max_requests: int = 64,
+                 use_cuda_graphs: bool = False):
         if model.device is None:
             raise StepError("the model has no weights bound")
         if model.device.type != "cuda":
@@ -91,6 +92,7 @@ class Engine:
         self._staging = _Staging(self.device)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # ---- request lifetime ------------------------------------------------------------
     def admit(self, rid: Hashable) -> int:
@@ -190,6 +192,7 @@ class Engine:
                 tv[s, :m] = bl[:m]
             table_slices[g.index] = ts
         dev[:total].copy_(host[:total], non_blocking=True)
+        self.last_h2d_bytes = 4 * total
         self._staging.sent(bi)
 
         def d(sl):
@@ -205,7 +208,7 @@ class Engine:
             max_q_len=max(q_lens), max_kv_len=max(b + n for b, n in zip(kv_before, q_lens)),
         )
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], reserved: bool = False) -> torch.Tensor:
         """Run one step; returns float32 logits [wanted, vocab] on the device.  The tensor
         is workspace memory: it is overwritten by the next step."""
         entries = [e for e in entries if len(e.tokens) > 0]
