@@ -216,11 +216,57 @@ def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, unif
 
 
 # --------------------------------------------------------------------------------------
+_kernel_status = {}
+
+
+def kernel_status(device) -> torch.Tensor:
+    """A device int the kernels with bounded waits raise bits in (0 = all waits were met)."""
+    key = torch.device(device).index or 0
+    t = _kernel_status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _kernel_status[key] = t
+    return t
+
+
+def check_kernel_status(device) -> None:
+    t = kernel_status(device)
+    code = int(t.item())
+    if code:
+        t.zero_()
+        raise KernelError(f"a kernel gave up waiting on a barrier (status {code}); its output is not valid")
+
+
 def tensor_core_gemm_supported(K: int, N: int) -> bool:
-    """Whether the tcgen05 kernel takes a [*, K] x [N, K] product (its operand rows must
-    start on 16-byte boundaries for TMA, so K must be a multiple of 8)."""
-    return False
+    """Whether the tcgen05 kernel takes a [*, K] x [N, K] product: its operand rows must start
+    on 16-byte boundaries for TMA, so K must be a multiple of 8."""
+    return K % 8 == 0 and K >= 8
 
 
-def gemm_tc(a, w, bias, out, *, act=None, residual=None) -> None:
-    raise KernelError("tensor-core gemm is not available")
+def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> None:
+    """out = act(a @ w.T + bias) + residual on the tcgen05 tensor cores.
+    a: bfloat16 [M, K]; w: bfloat16 [N, K]; out: bfloat16 or float32 [M, N]."""
+    _cuda(a, w, bias, out, residual)
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise UnsupportedShape("gemm_tc takes bfloat16 operands")
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_tc: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_tc: innermost stride must be 1")
+    if K % 8 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        raise UnsupportedShape(f"gemm_tc: K={K} and the row pitches must be multiples of 8 elements, "
+                               "operands 16-byte aligned")
+    if residual is not None and (residual.dtype != torch.float32 or residual.stride(1) != 1
+                                 or tuple(residual.shape) != (M, N)):
+        raise KernelError("gemm_tc: residual must be float32 [M, N]")
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N):
+        raise KernelError("gemm_tc: bias must be bfloat16 [N]")
+    lib = load_library("gemm_tc")
+    code = lib.sandy_gemm_tc(_p(a), _p(w), _p(bias), _p(residual), _p(out), ctypes.c_int(M), ctypes.c_int(N),
+                             ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
+                             ctypes.c_int(0 if residual is None else residual.stride(0)),
+                             ctypes.c_int(out.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(out)),
+                             ctypes.c_int(tile_n), _p(kernel_status(a.device)), _stream())
+    _check(code, f"gemm_tc(M={M},N={N},K={K})")

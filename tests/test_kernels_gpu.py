@@ -1,0 +1,161 @@
+"""Each kernel alone against a plain float32 reference of the same op, at sizes other than
+the engine's: odd widths, vocabularies that are no power of two, head sizes in steps of 16,
+head counts and groups that are no power of two."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def _gelu_new(u):
+    return 0.5 * u * (1 + torch.tanh(0.7978845608028654 * (u + 0.044715 * u ** 3)))
+
+
+def _act(u, act):
+    if act == "gelu_new":
+        return _gelu_new(u)
+    if act == "gelu":
+        return 0.5 * u * (1 + torch.erf(u / math.sqrt(2.0)))
+    return u
+
+
+# ---- embedding ---------------------------------------------------------------------------
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,vocab,npos", [(64, 512, 128), (240, 777, 33), (1600, 1000, 50)])
+def test_embed_positions(table_dtype, width, vocab, npos):
+    from sandyrt_b200.csrc import ops
+
+    wte, wpe = _rand((vocab, width), table_dtype, 1), _rand((npos, width), table_dtype, 2)
+    ids = torch.randint(0, vocab, (37,), dtype=torch.int32, device=DEV)
+    pos = torch.randint(0, npos, (37,), dtype=torch.int32, device=DEV)
+    out = torch.empty(37, width, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed_positions(ids, pos, wte, wpe, out, status=status)
+    want = wte.float()[ids.long()] + wpe.float()[pos.long()]
+    assert torch.equal(out, want) and int(status.item()) == 0
+    # no position table
+    ops.embed_positions(ids, pos, wte, None, out)
+    assert torch.equal(out, wte.float()[ids.long()])
+    # an id outside the table is reported, not read
+    ids[5] = vocab
+    ops.embed_positions(ids, pos, wte, wpe, out, status=status)
+    assert int(status.item()) & 1 and float(out[5].abs().sum()) == 0.0
+
+
+# ---- layernorm ----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtypes", [(torch.float32, torch.float32, torch.float32),
+                                    (torch.float32, torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("width,eps", [(64, 1e-5), (96, 1e-6), (240, 3e-5), (1600, 1e-5), (5000, 1e-3)])
+def test_layernorm(dtypes, width, eps):
+    from sandyrt_b200.csrc import ops
+
+    tin, tw, tout = dtypes
+    x = _rand((29, width), tin, 3, scale=3.0) + 1.5
+    g, b = _rand((width,), tw, 4) + 1.0, _rand((width,), tw, 5)
+    out = torch.empty(29, width, dtype=tout, device=DEV)
+    ops.layernorm(x, g, b, eps, out)
+    xd = x.double()
+    mean = xd.mean(-1, keepdim=True)
+    var = ((xd - mean) ** 2).mean(-1, keepdim=True)
+    want = ((xd - mean) / torch.sqrt(var + eps) * g.double() + b.double())
+    tol = 2e-5 if tout == torch.float32 else 2e-2
+    assert (out.double() - want).abs().max().item() < tol * (1 + want.abs().max().item())
+    # selected rows only
+    rows = torch.tensor([28, 0, 7, 7], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(4, width, dtype=tout, device=DEV)
+    ops.layernorm(x, g, b, eps, out2, rows=rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+# ---- matrix products ----------------------------------------------------------------------
+def _gemm_want(a, w_kn, bias, act, residual):
+    y = a.double() @ w_kn.double()
+    if bias is not None:
+        y = y + bias.double()
+    y = _act(y, act)
+    if residual is not None:
+        y = y + residual.double()
+    return y
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 192, 64), (33, 1000, 96), (130, 320, 96), (64, 777, 240), (7, 50, 13)])
+@pytest.mark.parametrize("layout", ["in_out", "out_in"])
+def test_gemm_simt(dtype, M, N, K, layout):
+    from sandyrt_b200.csrc import ops
+
+    a = _rand((M, K), dtype, 1)
+    w_kn = _rand((K, N), dtype, 2, scale=0.1)
+    bias = _rand((N,), dtype, 3)
+    res = _rand((M, N), torch.float32, 4)
+    w = w_kn if layout == "in_out" else w_kn.t().contiguous()
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
+    for act, use_res, out_dtype in ((None, False, dtype), ("gelu_new", False, dtype), ("gelu", False, dtype),
+                                    (None, True, torch.float32)):
+        if dtype == torch.float32 and out_dtype != torch.float32:
+            continue
+        out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        ops.gemm_simt(a, w, bias, out, w_out_in=(layout == "out_in"), act=act, residual=res if use_res else None)
+        want = _gemm_want(a, w_kn, bias, act, res if use_res else None)
+        err = (out.double() - want).abs().max().item()
+        assert err < tol * (1 + want.abs().max().item()), (act, use_res, err)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 2304, 768), (100, 777, 240), (128, 128, 64), (129, 130, 72),
+                                   (300, 1000, 96), (2048, 768, 3072), (257, 320, 96), (64, 50257, 64), (517, 96, 320)])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+def test_gemm_tc(M, N, K, tile_n):
+    """The tcgen05 kernel at sizes that are no multiple of its tiles, every epilogue."""
+    from sandyrt_b200.csrc import ops
+
+    a = _rand((M, K), torch.bfloat16, 1)
+    w_nk = _rand((N, K), torch.bfloat16, 2, scale=0.1)
+    bias = _rand((N,), torch.bfloat16, 3)
+    res = _rand((M, N), torch.float32, 4)
+    for act, use_res, out_dtype, use_bias in ((None, False, torch.bfloat16, True), ("gelu_new", False, torch.bfloat16, True),
+                                              ("gelu", False, torch.bfloat16, True), (None, True, torch.float32, True),
+                                              (None, False, torch.float32, False)):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        ops.gemm_tc(a, w_nk, bias if use_bias else None, out, act=act, residual=res if use_res else None, tile_n=tile_n)
+        ops.check_kernel_status(DEV)
+        want = _gemm_want(a, w_nk.t(), bias if use_bias else None, act, res if use_res else None)
+        tol = 1e-2 if out_dtype == torch.bfloat16 else 2e-5
+        err = (out.double() - want).abs().max().item()
+        assert err < tol * (1 + want.abs().max().item()), (act, use_res, out_dtype, err)
+
+
+def test_gemm_tc_in_place_residual_and_row_independence():
+    """out may be the residual itself; a row's result does not depend on the rows beside it."""
+    from sandyrt_b200.csrc import ops
+
+    a = _rand((200, 96), torch.bfloat16, 1)
+    w = _rand((96, 96), torch.bfloat16, 2, scale=0.1)
+    x = _rand((200, 96), torch.float32, 3)
+    want = x.double() + a.double() @ w.double().t()
+    ops.gemm_tc(a, w, None, x, residual=x)
+    assert (x.double() - want).abs().max().item() < 1e-4
+    full = torch.empty(200, 96, dtype=torch.float32, device=DEV)
+    ops.gemm_tc(a, w, None, full)
+    part = torch.empty(3, 96, dtype=torch.float32, device=DEV)
+    ops.gemm_tc(a[130:133].contiguous(), w, None, part)
+    assert torch.equal(part, full[130:133])
+
+
+def test_gemm_tc_refuses_what_it_cannot_take():
+    from sandyrt_b200.csrc import ops
+
+    a = _rand((4, 60), torch.bfloat16, 1)
+    w = _rand((16, 60), torch.bfloat16, 2)
+    out = torch.empty(4, 16, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.UnsupportedShape):
+        ops.gemm_tc(a, w, None, out)          # K = 60 is no multiple of 8
+    assert not ops.tensor_core_gemm_supported(60, 16)
