@@ -34,12 +34,20 @@ __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restric
                                  T* __restrict__ k_cache, T* __restrict__ v_cache, long long page_stride,
                                  const int* __restrict__ block_table, int max_blocks,
                                  const int* __restrict__ token_seq, const int* __restrict__ positions,
-                                 int n_kv_heads, int head_dim, int page_size) {
+                                 int n_kv_heads, int head_dim, int page_size, int num_pages,
+                                 int* __restrict__ status) {
     const int t = blockIdx.x;
     const int s = token_seq[t];
     const int pos = positions[t];
+    if (pos < 0 || pos / page_size >= max_blocks) {   // a position the block table does not cover
+        if (threadIdx.x == 0 && status) atomicOr(status, 8);
+        return;
+    }
     const int page = block_table[(size_t)s * max_blocks + pos / page_size];
-    if (page < 0) return;  // no page behind this position: nothing may be written
+    if (page < 0 || page >= num_pages) {              // no page behind this position: nothing may be written
+        if (threadIdx.x == 0 && status) atomicOr(status, 8);
+        return;
+    }
     const int slot = pos % page_size;
     const int n = n_kv_heads * head_dim;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -49,10 +57,6 @@ __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restric
         v_cache[dst] = v_src[(size_t)t * ld_src + i];
     }
 }
-
-template <typename T> struct Vec16;  // 16-byte vector of T
-template <> struct Vec16<float> { static constexpr int N = 4; };
-template <> struct Vec16<bf16> { static constexpr int N = 8; };
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const T* __restrict__ row, const float* __restrict__ q, int head_dim);
@@ -94,7 +98,7 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
                        const int* __restrict__ token_seq, const int* __restrict__ positions,
                        T* __restrict__ out, int ld_out,
                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                       float scale, int window) {
+                       float scale, int window, int num_pages, int* __restrict__ status) {
     __shared__ float q_smem[WARPS_PER_BLOCK][MAX_HEAD_DIM];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * WARPS_PER_BLOCK + warp;
@@ -122,13 +126,18 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
         long long row = 0;  // row index (units of D elements) of key j inside the layer's cache
         float sc = -INFINITY;
         if (valid) {
-            const int page = table[j / page_size];
-            row = (long long)page * rows_per_page + (long long)kvh * page_size + (j % page_size);
-            sc = dot_row<T>(k_cache + row * head_dim, qs, head_dim) * scale;
+            const int page = (j / page_size < max_blocks) ? table[j / page_size] : -1;
+            if (page < 0 || page >= num_pages) {
+                // a visible key with no page behind it: report it, read nothing
+                if (status) atomicOr(status, 16);
+            } else {
+                row = (long long)page * rows_per_page + (long long)kvh * page_size + (j % page_size);
+                sc = dot_row<T>(k_cache + row * head_dim, qs, head_dim) * scale;
+            }
         }
         const float m_new = fmaxf(m, warp_max(sc));
         const float corr = expf(m - m_new);   // first block: exp(-inf) = 0
-        const float p = valid ? expf(sc - m_new) : 0.0f;
+        const float p = (valid && sc > -INFINITY) ? expf(sc - m_new) : 0.0f;
         l = l * corr + warp_sum(p);
 #pragma unroll
         for (int i = 0; i < MAX_HEAD_DIM / 32; i++) acc[i] *= corr;
@@ -162,8 +171,8 @@ SANDY_API int sandy_kv_append(const void* k_src, const void* v_src, int ld_src,
                               void* k_cache, void* v_cache, long long page_stride,
                               const int* block_table, int max_blocks,
                               const int* token_seq, const int* positions,
-                              int n_tokens, int n_kv_heads, int head_dim, int page_size,
-                              int dtype, cudaStream_t stream) {
+                              int n_tokens, int n_kv_heads, int head_dim, int page_size, int num_pages,
+                              int dtype, int* status, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!k_src || !v_src || !k_cache || !v_cache || !block_table || !token_seq || !positions)
         return SANDY_ERR_ARGUMENT;
@@ -172,11 +181,11 @@ SANDY_API int sandy_kv_append(const void* k_src, const void* v_src, int ld_src,
     if (dtype == SANDY_F32)
         kv_append_kernel<float><<<n_tokens, threads, 0, stream>>>(
             (const float*)k_src, (const float*)v_src, ld_src, (float*)k_cache, (float*)v_cache, page_stride,
-            block_table, max_blocks, token_seq, positions, n_kv_heads, head_dim, page_size);
+            block_table, max_blocks, token_seq, positions, n_kv_heads, head_dim, page_size, num_pages, status);
     else if (dtype == SANDY_BF16)
         kv_append_kernel<bf16><<<n_tokens, threads, 0, stream>>>(
             (const bf16*)k_src, (const bf16*)v_src, ld_src, (bf16*)k_cache, (bf16*)v_cache, page_stride,
-            block_table, max_blocks, token_seq, positions, n_kv_heads, head_dim, page_size);
+            block_table, max_blocks, token_seq, positions, n_kv_heads, head_dim, page_size, num_pages, status);
     else
         return SANDY_ERR_UNSUPPORTED;
     return sandy_launch_status();
@@ -188,7 +197,8 @@ SANDY_API int sandy_paged_attention(const void* q, int ld_q, const void* k_cache
                                     long long page_stride, const int* block_table, int max_blocks,
                                     const int* token_seq, const int* positions, void* out, int ld_out,
                                     int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                    float scale, int window, int dtype, cudaStream_t stream) {
+                                    float scale, int window, int num_pages, int dtype, int* status,
+                                    cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out)
         return SANDY_ERR_ARGUMENT;
@@ -201,7 +211,7 @@ SANDY_API int sandy_paged_attention(const void* q, int ld_q, const void* k_cache
     paged_attention_kernel<T><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(                           \
         (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, \
         token_seq, positions, (T*)out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size,    \
-        scale, window)
+        scale, window, num_pages, status)
     if (dtype == SANDY_F32) LAUNCH(float);
     else if (dtype == SANDY_BF16) LAUNCH(bf16);
     else return SANDY_ERR_UNSUPPORTED;

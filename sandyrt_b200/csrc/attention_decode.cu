@@ -1,0 +1,245 @@
+// Attention of single tokens over long cached contexts, with the keys of one (token, head)
+// pair split over several thread blocks ("split-KV"), then merged.
+//
+// Formula as in attention.cu (src/core/TensorCalc.cpp:1241-1311 of the reference); the
+// reference's decode pair of kernels does the same split and merge
+// (flash_attention_decode_partial/reduce, src/device/cuda/CudaAttentionKernels.cu:246-404:
+// one warp per split, a scratch of (D + 2) floats per split that it allocates on every
+// call, :496-503).  Differences here: the scratch is the caller's (allocated once, reused by
+// every layer and step); a block is four warps that read keys and values in 16-byte pieces,
+// several lanes per key, so that every load instruction of a warp covers whole rows; the
+// block table of the token's request is walked directly; and the number of splits is fixed
+// by the caller per launch shape, so the launch can be recorded in a CUDA graph.
+//
+// Block (split, head, token): keys [lo + split*chunk, ...) of the token's visible range
+// [lo, pos].  Each group of LPK lanes owns one key per round and keeps its own running
+// (max, sum, weighted values); the groups are merged in shared memory in a fixed order, and
+// the block writes either the final output (one split) or its partial state
+// (max, sum, unnormalised output) to the scratch.  A second kernel merges the splits.
+// Scores, softmax and sums are float.
+//
+// Head sizes: D * sizeof(T) / 16 must divide 32 (D = 16, 32, 64, 128, and 256 in bfloat16).
+// Other head sizes are served by the general kernel in attention.cu.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int UNROLL = 4;
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T* p, float (&f)[VEC]);
+
+template <>
+__device__ __forceinline__ void load_vec<float, 4>(const float* p, float (&f)[4]) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+
+template <>
+__device__ __forceinline__ void load_vec<bf16, 8>(const bf16* p, float (&f)[8]) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k_cache,
+                        const T* __restrict__ v_cache, long long page_stride,
+                        const int* __restrict__ block_table, int max_blocks,
+                        const int* __restrict__ token_seq, const int* __restrict__ positions,
+                        T* __restrict__ out, int ld_out, float* __restrict__ partial_o,
+                        float* __restrict__ partial_ml, int n_heads, int n_kv_heads, int page_size,
+                        float scale, int window, int num_splits, int num_pages, int* __restrict__ status) {
+    constexpr int VEC = 16 / sizeof(T);         // elements per 16-byte piece
+    constexpr int LPK = D / VEC;                // lanes per key
+    constexpr int KPW = 32 / LPK;               // keys per warp per round
+    constexpr int GROUPS = WARPS * KPW;
+    static_assert(LPK >= 1 && LPK <= 32 && (32 % LPK) == 0, "head size not supported by this kernel");
+
+    __shared__ float sm_m[GROUPS], sm_l[GROUPS];
+    __shared__ float sm_o[GROUPS][D];
+
+    const int split = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane / LPK, sub = lane % LPK;
+    const int group = warp * KPW + g;
+    const int s = token_seq[t];
+    const int pos = positions[t];
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+    const int n_keys = pos - lo + 1;
+    int chunk = (n_keys + num_splits - 1) / num_splits;
+    chunk = (chunk + GROUPS - 1) / GROUPS * GROUPS;
+    const int begin = lo + split * chunk;
+    const int end = min(pos + 1, begin + chunk);
+    const int* table = block_table + (size_t)s * max_blocks;
+
+    float qf[VEC];
+    load_vec<T, VEC>(q + (size_t)t * ld_q + h * D + sub * VEC, qf);
+
+    float m = -INFINITY, l = 0.0f;
+    float o[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; i++) o[i] = 0.0f;
+
+    for (int j0 = begin + group; j0 < end; j0 += GROUPS * UNROLL) {
+        float kf[UNROLL][VEC], vf[UNROLL][VEC];
+        bool ok[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const int j = j0 + u * GROUPS;
+            ok[u] = j < end;
+            if (ok[u]) {
+                const int b = j / page_size;
+                const int page = b < max_blocks ? table[b] : -1;
+                if (page < 0 || page >= num_pages) {
+                    if (status && sub == 0) atomicOr(status, 16);   // a visible key with no page behind it
+                    ok[u] = false;
+                } else {
+                    const size_t off = (size_t)page * page_stride +
+                                       ((size_t)kvh * page_size + (j % page_size)) * D + sub * VEC;
+                    load_vec<T, VEC>(k_cache + off, kf[u]);
+                    load_vec<T, VEC>(v_cache + off, vf[u]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            float sc = 0.0f;
+            if (ok[u]) {
+#pragma unroll
+                for (int i = 0; i < VEC; i++) sc = fmaf(qf[i], kf[u][i], sc);
+            }
+#pragma unroll
+            for (int w = LPK / 2; w > 0; w >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, w);
+            if (ok[u]) {          // uniform across the LPK lanes of the group
+                sc *= scale;
+                const float m_new = fmaxf(m, sc);
+                const float corr = expf(m - m_new);
+                const float p = expf(sc - m_new);
+                l = l * corr + p;
+#pragma unroll
+                for (int i = 0; i < VEC; i++) o[i] = fmaf(p, vf[u][i], o[i] * corr);
+                m = m_new;
+            }
+        }
+    }
+
+    if (sub == 0) {
+        sm_m[group] = m;
+        sm_l[group] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; i++) sm_o[group][sub * VEC + i] = o[i];
+    __syncthreads();
+
+    // merge the groups, one thread per output dimension, fixed order
+    for (int d = threadIdx.x; d < D; d += WARPS * 32) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < GROUPS; i++) M = fmaxf(M, sm_m[i]);
+        float L = 0.0f, O = 0.0f;
+        if (M > -INFINITY) {
+#pragma unroll
+            for (int i = 0; i < GROUPS; i++) {
+                const float w = expf(sm_m[i] - M);     // exp(-inf) = 0 for groups that saw no key
+                L = fmaf(sm_l[i], w, L);
+                O = fmaf(sm_o[i][d], w, O);
+            }
+        }
+        if (num_splits == 1) {
+            out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+        } else {
+            const size_t slot = ((size_t)t * n_heads + h) * num_splits + split;
+            partial_o[slot * D + d] = O;
+            if (d == 0) {
+                partial_ml[slot * 2] = M;
+                partial_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+template <typename T, int D>
+__global__ void merge_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                                    T* __restrict__ out, int ld_out, int n_heads, int num_splits) {
+    const int h = blockIdx.x, t = blockIdx.y;
+    const size_t base = ((size_t)t * n_heads + h) * num_splits;
+    float M = -INFINITY;
+    for (int i = 0; i < num_splits; i++) M = fmaxf(M, partial_ml[(base + i) * 2]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float L = 0.0f, O = 0.0f;
+        if (M > -INFINITY) {
+            for (int i = 0; i < num_splits; i++) {
+                const float w = expf(partial_ml[(base + i) * 2] - M);
+                L = fmaf(partial_ml[(base + i) * 2 + 1], w, L);
+                O = fmaf(partial_o[(base + i) * D + d], w, O);
+            }
+        }
+        out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+    }
+}
+
+template <typename T, int D>
+int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+           const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
+           int ld_out, float* scratch, int n_tokens, int n_heads, int n_kv_heads, int page_size, float scale,
+           int window, int num_splits, int num_pages, int* status, cudaStream_t stream) {
+    float* partial_o = scratch;
+    float* partial_ml = scratch ? scratch + (size_t)n_tokens * n_heads * num_splits * D : nullptr;
+    dim3 grid(num_splits, n_heads, n_tokens);
+    decode_attention_kernel<T, D><<<grid, WARPS * 32, 0, stream>>>(
+        (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, token_seq,
+        positions, (T*)out, ld_out, partial_o, partial_ml, n_heads, n_kv_heads, page_size, scale, window,
+        num_splits, num_pages, status);
+    int code = sandy_launch_status();
+    if (code != 0 || num_splits == 1) return code;
+    merge_splits_kernel<T, D><<<dim3(n_heads, n_tokens), D < 32 ? 32 : (D > 256 ? 256 : D), 0, stream>>>(
+        partial_o, partial_ml, (T*)out, ld_out, n_heads, num_splits);
+    return sandy_launch_status();
+}
+
+}  // namespace
+
+// Floats of scratch the split kernel needs for this shape (0 when num_splits == 1).
+SANDY_API long long sandy_decode_attention_scratch_floats(int n_tokens, int n_heads, int head_dim, int num_splits) {
+    if (num_splits <= 1) return 0;
+    return (long long)n_tokens * n_heads * num_splits * (head_dim + 2);
+}
+
+// q, out: [n_tokens, H*D] (row strides ld_q, ld_out); caches as in attention.cu; scratch: float
+// array of sandy_decode_attention_scratch_floats(...) elements (may be null for one split).
+SANDY_API int sandy_decode_attention(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                     long long page_stride, const int* block_table, int max_blocks,
+                                     const int* token_seq, const int* positions, void* out, int ld_out,
+                                     float* scratch, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                     int page_size, float scale, int window, int num_splits, int num_pages,
+                                     int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out) return SANDY_ERR_ARGUMENT;
+    if (num_splits < 1 || (num_splits > 1 && !scratch)) return SANDY_ERR_ARGUMENT;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0) return SANDY_ERR_UNSUPPORTED;
+    if (n_heads > 65535 || n_tokens > 65535) return SANDY_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
+        (reinterpret_cast<uintptr_t>(v_cache) & 15))
+        return SANDY_ERR_UNSUPPORTED;
+    const int esz = dtype == SANDY_F32 ? 4 : 2;
+    if ((ld_q * esz) % 16 != 0 || (page_stride * esz) % 16 != 0) return SANDY_ERR_UNSUPPORTED;
+#define CASE(DT, TT, DD)                                                                                    \
+    if (dtype == DT && head_dim == DD)                                                                      \
+        return launch<TT, DD>(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq,   \
+                              positions, out, ld_out, scratch, n_tokens, n_heads, n_kv_heads, page_size,    \
+                              scale, window, num_splits, num_pages, status, stream)
+    CASE(SANDY_BF16, bf16, 16); CASE(SANDY_BF16, bf16, 32); CASE(SANDY_BF16, bf16, 64);
+    CASE(SANDY_BF16, bf16, 128); CASE(SANDY_BF16, bf16, 256);
+    CASE(SANDY_F32, float, 16); CASE(SANDY_F32, float, 32); CASE(SANDY_F32, float, 64); CASE(SANDY_F32, float, 128);
+#undef CASE
+    return SANDY_ERR_UNSUPPORTED;
+}

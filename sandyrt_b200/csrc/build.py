@@ -38,7 +38,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_simt": [],
     "gemm_tc": [],
     "attention": [],
-    "attention_tc": [],
+    "attention_decode": [],
+    "attention_prefill": [],
     "sampling": [],
 }
 

@@ -145,13 +145,13 @@ def _cache_args(k_cache, v_cache):
     want = (k_cache.stride(0), ps * d, d, 1)
     if tuple(k_cache.stride()) != want or tuple(v_cache.stride()) != want:
         raise KernelError("cache views must be dense inside a page")
-    return hkv, ps, d, k_cache.stride(0)
+    return hkv, ps, d, k_cache.stride(0), k_cache.shape[0]
 
 
 def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions) -> None:
     """Write the step's keys/values ([T, Hkv*D] views, one row stride) into their pages."""
     _cuda(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
-    hkv, ps, d, page_stride = _cache_args(k_cache, v_cache)
+    hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = k_src.shape[0]
     if k_src.shape != v_src.shape or k_src.shape[1] != hkv * d or k_src.stride() != v_src.stride() \
             or k_src.stride(1) != 1 or k_src.dtype != k_cache.dtype:
@@ -161,7 +161,8 @@ def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
     code = lib.sandy_kv_append(_p(k_src), _p(v_src), ctypes.c_int(k_src.stride(0)), _p(k_cache), _p(v_cache),
                                ctypes.c_longlong(page_stride), _p(block_table), ctypes.c_int(block_table.shape[1]),
                                _p(token_seq), _p(positions), ctypes.c_int(T), ctypes.c_int(hkv), ctypes.c_int(d),
-                               ctypes.c_int(ps), ctypes.c_int(_dt(k_cache)), _stream())
+                               ctypes.c_int(ps), ctypes.c_int(num_pages), ctypes.c_int(_dt(k_cache)),
+                               _p(kernel_status(k_cache.device)), _stream())
     _check(code, "kv_append")
 
 
@@ -169,7 +170,7 @@ def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out,
                     n_heads: int, scale: float, window: int = 0) -> None:
     """Causal attention of every token of the step over its request's pages (general kernel)."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
-    hkv, ps, d, page_stride = _cache_args(k_cache, v_cache)
+    hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
     if d % 16 != 0 or d > 256:
         raise UnsupportedShape(f"attention: head size {d} must be a multiple of 16, at most 256")
@@ -185,12 +186,68 @@ def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out,
                                      ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
                                      ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads),
                                      ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale),
-                                     ctypes.c_int(window), ctypes.c_int(_dt(q)), _stream())
+                                     ctypes.c_int(window), ctypes.c_int(num_pages), ctypes.c_int(_dt(q)),
+                                     _p(kernel_status(q.device)), _stream())
     _check(code, f"paged_attention(H={n_heads},Hkv={hkv},D={d})")
+
+
+_DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
+
+
+def decode_splits(n_tokens: int, n_heads: int, max_kv: int) -> int:
+    """How many blocks share the keys of one (token, head) pair: enough to fill the GPU's 148
+    SMs a few times over, but no block with fewer than 64 keys.  It depends on the launch
+    shape only (not on the requests' exact lengths), so a recorded graph stays valid."""
+    want = -(-4 * 148 // max(1, n_tokens * n_heads))
+    cap = max(1, max_kv // 64)
+    return max(1, min(want, cap, 32))
+
+
+def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int,
+                     scale: float, window: int = 0, num_splits: int = 1, scratch=None) -> None:
+    """Split-KV attention of single tokens (head sizes 16/32/64/128, 256 in bfloat16)."""
+    _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, scratch)
+    hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
+    T = q.shape[0]
+    if d not in _DECODE_HEAD_DIMS.get(q.dtype, ()):
+        raise UnsupportedShape(f"decode_attention: head size {d} in {q.dtype} is not supported by this kernel")
+    if n_heads % hkv != 0:
+        raise UnsupportedShape(f"attention: {n_heads} heads do not divide into {hkv} key/value heads")
+    if q.shape[1] != n_heads * d or out.shape != q.shape or q.stride(1) != 1 or out.stride(1) != 1 \
+            or q.dtype != k_cache.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
+    _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
+    need = T * n_heads * num_splits * (d + 2) if num_splits > 1 else 0
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need
+                 or not scratch.is_contiguous()):
+        raise KernelError(f"decode_attention: {num_splits} splits need a float32 scratch of {need} elements")
+    lib = load_library("attention_decode")
+    code = lib.sandy_decode_attention(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+                                      ctypes.c_longlong(page_stride), _p(block_table),
+                                      ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
+                                      ctypes.c_int(out.stride(0)), _p(scratch), ctypes.c_int(T), ctypes.c_int(n_heads),
+                                      ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale),
+                                      ctypes.c_int(window), ctypes.c_int(num_splits), ctypes.c_int(num_pages),
+                                      ctypes.c_int(_dt(q)), _p(kernel_status(q.device)), _stream())
+    _check(code, f"decode_attention(H={n_heads},Hkv={hkv},D={d},splits={num_splits})")
+    if num_splits > 1:
+        global LAUNCHES
+        LAUNCHES += 1
 
 
 def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale: float, window: int = 0) -> None:
     """Attention of a step's tokens over the cache: picks the kernel for the step's shape."""
+    d = k_cache.shape[3]
+    if ctx.max_q_len == 1 and d in _DECODE_HEAD_DIMS.get(q.dtype, ()):
+        max_kv = block_table.shape[1] * k_cache.shape[2]
+        splits = decode_splits(ctx.n_tokens, n_heads, max_kv)
+        scratch = None
+        if splits > 1:
+            scratch = ctx.workspace.get("attention_splits", 1, ctx.n_tokens * n_heads * splits * (d + 2),
+                                        torch.float32).view(-1)
+        decode_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out, n_heads=n_heads,
+                         scale=scale, window=window, num_splits=splits, scratch=scratch)
+        return
     paged_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out,
                     n_heads=n_heads, scale=scale, window=window)
 
@@ -234,7 +291,9 @@ def check_kernel_status(device) -> None:
     code = int(t.item())
     if code:
         t.zero_()
-        raise KernelError(f"a kernel gave up waiting on a barrier (status {code}); its output is not valid")
+        raise KernelError(f"a kernel reported a fault (status {code}: bits 0-2 a barrier wait ran out in the "
+                          "tensor-core product, bit 3 a key/value write and bit 4 a key read had no page behind "
+                          "it); the step's output is not valid")
 
 
 def tensor_core_gemm_supported(K: int, N: int) -> bool:

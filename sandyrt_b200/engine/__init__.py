@@ -1,1 +1,1 @@
-from .step import Engine, StepEntry, StepError  # noqa: F401
+from .step import Engine, SampleRow, StepEntry, StepError  # noqa: F401

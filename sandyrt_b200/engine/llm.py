@@ -25,9 +25,9 @@ import torch
 
 from ..models.model import Model, load_model
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler, fresh_seed
+from ..sampling.sampler import fresh_seed, uniform_for
 from .scheduler import Request, RequestRefused, RequestState, Scheduler, StepPlan
-from .step import Engine, StepEntry
+from .step import Engine, SampleRow, StepEntry
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -73,11 +73,10 @@ class LLM:
         if cache_tokens is None:
             cache_tokens = min(max_live * (limit or 4096), 1 << 20)
         self.engine = Engine(self.model, max_tokens=cache_tokens, page_size=page_size, max_requests=max_live,
-                             use_cuda_graphs=use_cuda_graphs)
+                             max_step_tokens=max_step_tokens, use_cuda_graphs=use_cuda_graphs)
         self.scheduler = Scheduler(self.engine.cache.alloc, max_step_tokens=max_step_tokens,
                                    prefill_chunk=prefill_chunk_tokens, max_live=max_live,
                                    max_positions=limit)
-        self.sampler = Sampler(self.model.device)
         self.eos_token_ids = frozenset(int(t) for t in (eos_token_ids or ()))
         self._requests: Dict[Hashable, Request] = {}
         self._seeds: Dict[Hashable, int] = {}
@@ -124,20 +123,24 @@ class LLM:
             entries.append(StepEntry(req.rid, toks, [p.count - 1] if p.samples else []))
             if p.samples:
                 sampled_reqs.append(req)
-        logits = self.engine.step(entries, reserved=True)
+        rows = []
+        for r in sampled_reqs:
+            sp = r.sampling
+            rows.append(SampleRow(0.0 if sp.greedy else sp.temperature, sp.top_k, sp.top_p,
+                                  0.0 if sp.greedy else uniform_for(self._seeds[r.rid], len(r.output))))
+        self.engine.step(entries, sampling=rows, reserved=True)
         sampled: Dict[Hashable, int] = {}
         if sampled_reqs:
             n = len(sampled_reqs)
-            tokens = self.sampler.sample(
-                logits, [r.sampling for r in sampled_reqs], [self._seeds[r.rid] for r in sampled_reqs],
-                [len(r.output) for r in sampled_reqs])
+            tokens = self.engine.sampled_tokens(n)
             if self._token_host.numel() < n:
                 self._token_host = torch.empty(n, dtype=torch.int32, pin_memory=True)
             self._token_host[:n].copy_(tokens, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             host = self._token_host[:n].tolist()
             if any(t < 0 for t in host):
-                self.sampler.check_status()
+                self.engine.check_status()
+                raise ValueError("sampling logits must not contain NaN")     # Sampler.cpp:64-67
             sampled = {r.rid: t for r, t in zip(sampled_reqs, host)}
         now = time.perf_counter()
         for r in sampled_reqs:

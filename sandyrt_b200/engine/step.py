@@ -5,28 +5,32 @@ the request already has in the cache (a portion of a prompt of any length, or on
 token) and the places among them whose logits are wanted.  It runs exactly those tokens as
 one batch, reading everything earlier from the cache, appends their keys and values to the
 cache, and returns float32 logits [wanted, vocab] in the order of the entries and of their
-wanted places.
+wanted places.  With `sampling` it also draws one token per wanted row on the device.
 
 The reference's counterpart, Engine::runValues on one of two compiled graphs (decode with
 input_id [1,1], prefill with input_id [1,n]; src/engine/Engine.h:100-104,
 src/server/Model.cpp:216-255, inputs built in src/server/Session.cpp:167-206), serves one
-request per call and returns logits for every row.  Here there is one code path for every
-mix of requests, and rows nobody asked for are never computed past the last layer.
+request per call, returns logits for every row and samples on the host.  Here there is one
+code path for every mix of requests, and rows nobody asked for are never computed past the
+last layer.
 
 All the step's index arrays (token ids, positions, request of each token, block tables,
-wanted rows) are packed on the host into one pinned buffer and reach the device with one
-copy.
+wanted rows, sampling options) are packed on the host into one pinned buffer and reach the
+device with one copy.  Steps in which every request brings a single token (decoding) are
+captured as CUDA graphs, one per (requests, wanted rows, block-table width), and replayed:
+the arrays live at fixed device addresses, so a replay only needs the copy before it.
 """
 from __future__ import annotations
 
 import dataclasses
-from typing import Dict, Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pages import FREED, OutOfPages
+from ..csrc import ops
 from ..models.model import Model
 from ..parts.base import StepContext, Workspace
 
@@ -39,45 +43,59 @@ class StepEntry:
     want: Sequence[int] = ()        # indices into `tokens` whose logits are returned
 
 
+@dataclasses.dataclass
+class SampleRow:
+    """How the token of one wanted row is drawn (see sampling.params.SamplingParams)."""
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    uniform: float = 0.0
+
+
 class StepError(Exception):
     pass
 
 
 class _Staging:
-    """A ring of pinned host buffers and one device buffer for the step's index arrays."""
+    """A ring of pinned host buffers and ONE device buffer for the step's index arrays.  The
+    device buffer keeps its address for the engine's lifetime unless a step outgrows it."""
 
-    def __init__(self, device, depth: int = 4):
+    def __init__(self, device, capacity: int, depth: int = 4):
         self.device = device
         self.depth = depth
-        self.capacity = 0
-        self.host: List[torch.Tensor] = []
-        self.events: List[Optional[torch.cuda.Event]] = []
-        self.dev: Optional[torch.Tensor] = None
         self.turn = 0
+        self.generation = 0
+        self._allocate(capacity)
 
-    def acquire(self, n: int):
+    def _allocate(self, capacity: int) -> None:
+        self.capacity = capacity
+        self.host = [torch.empty(capacity, dtype=torch.int32, pin_memory=True) for _ in range(self.depth)]
+        self.host_np = [h.numpy() for h in self.host]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * self.depth
+        self.dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
+        self.generation += 1
+
+    def acquire(self, n: int) -> int:
         if n > self.capacity:
-            self.capacity = max(1024, 1 << (n - 1).bit_length())
-            self.host = [torch.empty(self.capacity, dtype=torch.int32, pin_memory=True) for _ in range(self.depth)]
-            self.events = [None] * self.depth
-            self.dev = torch.empty(self.capacity, dtype=torch.int32, device=self.device)
+            self._allocate(1 << (n - 1).bit_length())
         i = self.turn
         self.turn = (self.turn + 1) % self.depth
         if self.events[i] is not None:
             self.events[i].synchronize()      # the copy that last used this buffer is done
-        return i, self.host[i], self.dev
+        return i
 
-    def sent(self, i: int) -> None:
-        ev = torch.cuda.Event()
-        ev.record()
-        self.events[i] = ev
+    def send(self, i: int, n: int) -> None:
+        self.dev[:n].copy_(self.host[i][:n], non_blocking=True)
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
 
 
 class Engine:
     """A bound model, its cache and the step function over them."""
 
     def __init__(self, model: Model, *, max_tokens: int, page_size: int = 16, max_requests: int = 64,
-                 use_cuda_graphs: bool = False):
+                 max_step_tokens: int = 2048, use_cuda_graphs: bool = True):
         if model.device is None:
             raise StepError("the model has no weights bound")
         if model.device.type != "cuda":
@@ -89,10 +107,20 @@ class Engine:
         self.cache = CacheManager(model.cache_specs(), page_size=page_size, max_tokens=max_tokens,
                                   max_requests=max_requests, device=self.device, dtype=self.dtype)
         self.workspace = Workspace(self.device)
-        self._staging = _Staging(self.device)
+        blocks_cap = -(-(model.max_positions or max_tokens) // page_size) + 8
+        cap = 4 * max_step_tokens + 3 * max_requests + 1 + 4 * max_requests \
+            + len(self.cache.layout.groups) * max_requests * blocks_cap
+        self._staging = _Staging(self.device, 1 << (cap - 1).bit_length())
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._sampled = torch.zeros(max(max_requests, 1), dtype=torch.int32, device=self.device)
+        self.use_cuda_graphs = use_cuda_graphs
+        self._graphs: Dict[Tuple, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._seen: Dict[Tuple, int] = {}
         self.steps_run = 0
+        self.graph_replays = 0
+        self.stale_graphs = 0
         self.last_h2d_bytes = 0
+        self.last_launches = 0
 
     # ---- request lifetime ------------------------------------------------------------
     def admit(self, rid: Hashable) -> int:
@@ -105,14 +133,14 @@ class Engine:
         return self.cache.alloc.length(rid)
 
     # ---- the step --------------------------------------------------------------------
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Reserve pages, pack the step's index arrays and copy them to the device."""
+    def _prepare(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]]):
+        """Check the entries, reserve pages, pack the step's arrays and copy them to the device."""
         alloc = self.cache.alloc
-        entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             raise StepError("a step needs at least one token")
         seen = set()
         q_lens, kv_before, slots = [], [], []
+        limit = self.model.max_positions
         for e in entries:
             if e.rid in seen:
                 raise StepError(f"request {e.rid!r} appears twice in one step")
@@ -121,15 +149,8 @@ class Engine:
                 self.admit(e.rid)
             before = alloc.length(e.rid)
             n = len(e.tokens)
-            limit = self.model.max_positions
             if limit is not None and before + n > limit:
                 raise StepError(f"request {e.rid!r}: {before + n} tokens exceed the model's {limit} positions")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab_size):
-                    raise StepError(f"request {e.rid!r}: token id {t} is outside the vocabulary of {self.vocab_size}")
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise StepError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
             q_lens.append(n)
             kv_before.append(before)
             slots.append(alloc.slot(e.rid))
@@ -146,20 +167,25 @@ class Engine:
             alloc.reserve(e.rid, before + n)
 
         T, S = sum(q_lens), len(entries)
-        groups = self.cache.layout.groups
-        max_blocks = max(1, max(-(-(b + n) // self.cache.page_size) for b, n in zip(kv_before, q_lens)))
         R = sum(len(e.want) for e in entries)
-        total = 3 * T + S + (S + 1) + S + R + len(groups) * S * max_blocks
-        bi, host, dev = self._staging.acquire(total)
-        h = host.numpy()
+        if sampling is not None and len(sampling) != R:
+            raise StepError(f"{len(sampling)} sampling rows for {R} wanted places")
+        groups = self.cache.layout.groups
+        decode_only = max(q_lens) == 1
+        max_blocks = max(-(-(b + n) // self.cache.page_size) for b, n in zip(kv_before, q_lens))
+        max_blocks = max(8, -(-max_blocks // 8) * 8)      # widths in steps of 8: few distinct graphs
+        n_sample = 4 * R if sampling is not None else 0
+        total = 3 * T + S + (S + 1) + S + R + n_sample + len(groups) * S * max_blocks
+        bi = self._staging.acquire(total)
+        h = self._staging.host_np[bi]
+        dev = self._staging.dev
         off = 0
 
         def take(n):
             nonlocal off
-            view = h[off:off + n]
             sl = (off, n)
             off += n
-            return view, sl
+            return h[sl[0]:sl[0] + n], sl
 
         ids_v, ids_s = take(T)
         pos_v, pos_s = take(T)
@@ -169,18 +195,33 @@ class Engine:
         kvb_v, kvb_s = take(S)
         rows_v, rows_s = take(R)
         t0, r0 = 0, 0
+        vocab = self.vocab_size
         for s, (e, n, before) in enumerate(zip(entries, q_lens, kv_before)):
-            ids_v[t0:t0 + n] = np.asarray(e.tokens, dtype=np.int32)
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.min() < 0 or toks.max() >= vocab:
+                raise StepError(f"request {e.rid!r}: a token id is outside the vocabulary of {vocab}")
+            ids_v[t0:t0 + n] = toks
             pos_v[t0:t0 + n] = np.arange(before, before + n, dtype=np.int32)
             seq_v[t0:t0 + n] = s
             qs_v[s] = t0
             for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
                 rows_v[r0] = t0 + int(w)
                 r0 += 1
             t0 += n
         qs_v[S] = T
         slot_v[:] = slots
         kvb_v[:] = kv_before
+        sample_s = None
+        if sampling is not None:
+            sv, sample_s = take(4 * R)
+            fv = sv.view(np.float32)
+            for i, row in enumerate(sampling):
+                fv[i] = row.temperature
+                sv[R + i] = row.top_k
+                fv[2 * R + i] = row.top_p
+                fv[3 * R + i] = row.uniform
         table_slices = {}
         for g in groups:
             tv, ts = take(S * max_blocks)
@@ -191,14 +232,13 @@ class Engine:
                 m = min(len(bl), max_blocks)
                 tv[s, :m] = bl[:m]
             table_slices[g.index] = ts
-        dev[:total].copy_(host[:total], non_blocking=True)
+        self._staging.send(bi, total)
         self.last_h2d_bytes = 4 * total
-        self._staging.sent(bi)
 
         def d(sl):
             return dev[sl[0]:sl[0] + sl[1]]
 
-        return StepContext(
+        ctx = StepContext(
             n_tokens=T, n_seqs=S,
             token_ids=d(ids_s), positions=d(pos_s), token_seq=d(seq_s), seq_slots=d(slot_s),
             q_start=d(qs_s), kv_before=d(kvb_s), logit_rows=d(rows_s),
@@ -207,21 +247,73 @@ class Engine:
             host_q_lens=q_lens, host_kv_before=kv_before, host_slots=slots,
             max_q_len=max(q_lens), max_kv_len=max(b + n for b, n in zip(kv_before, q_lens)),
         )
+        sample_dev = d(sample_s) if sample_s is not None else None
+        key = (T, S, R, max_blocks, sampling is not None, self._staging.generation) if decode_only else None
+        return ctx, sample_dev, key
 
-    def step(self, entries: Sequence[StepEntry], reserved: bool = False) -> torch.Tensor:
-        """Run one step; returns float32 logits [wanted, vocab] on the device.  The tensor
-        is workspace memory: it is overwritten by the next step."""
-        entries = [e for e in entries if len(e.tokens) > 0]
-        ctx = self.build_context(entries)
+    def _run(self, ctx: StepContext, sample_dev: Optional[torch.Tensor]) -> torch.Tensor:
         logits = self.model.forward(ctx, status=self._status)
-        for e, n, before in zip(entries, ctx.host_q_lens, ctx.host_kv_before):
-            self.cache.alloc.commit(e.rid, before + n)
+        R = ctx.logit_rows.numel()
+        if sample_dev is not None and R:
+            f = sample_dev.view(torch.float32)
+            ops.sample(logits, self._sampled[:R], temperature=f[:R], top_k=sample_dev[R:2 * R],
+                       top_p=f[2 * R:3 * R], uniform=f[3 * R:4 * R], status=self._status)
+        return logits
+
+    def step(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]] = None,
+             reserved: bool = False) -> torch.Tensor:
+        """Run one step; returns float32 logits [wanted, vocab] on the device.  The tensor is
+        workspace memory: the next step overwrites it.  With `sampling` (one SampleRow per
+        wanted place) the drawn tokens are in `self.sampled_tokens(n)` afterwards."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        ctx, sample_dev, key = self._prepare(entries, sampling)
+        R = ctx.logit_rows.numel()
+        if self._sampled.numel() < R:
+            self._sampled = torch.zeros(R, dtype=torch.int32, device=self.device)
+        before = ops.LAUNCHES
+        if key is not None and self.use_cuda_graphs:
+            hit = self._graphs.get(key)
+            if hit is not None and hit[3] != self.workspace.version:
+                # a workspace buffer has moved since this graph was recorded: its pointers are stale
+                del self._graphs[key]
+                self._seen.pop(key, None)
+                hit = None
+                self.stale_graphs += 1
+            if hit is not None:
+                hit[0].replay()
+                logits = hit[1]
+                self.graph_replays += 1
+                self.last_launches = hit[2]
+            elif self._seen.get(key, 0) >= 1:
+                # the second time a shape comes by it is recorded; the record is then run
+                torch.cuda.current_stream().synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    logits = self._run(ctx, sample_dev)
+                n_launch = ops.LAUNCHES - before
+                self._graphs[key] = (graph, logits, n_launch, self.workspace.version)
+                graph.replay()
+                self.last_launches = n_launch
+            else:
+                self._seen[key] = 1
+                logits = self._run(ctx, sample_dev)
+                self.last_launches = ops.LAUNCHES - before
+        else:
+            logits = self._run(ctx, sample_dev)
+            self.last_launches = ops.LAUNCHES - before
+        for e, n, b in zip(entries, ctx.host_q_lens, ctx.host_kv_before):
+            self.cache.alloc.commit(e.rid, b + n)
         self.steps_run += 1
         return logits
 
+    def sampled_tokens(self, n: int) -> torch.Tensor:
+        """The tokens drawn by the last step with `sampling` (int32 [n] on the device)."""
+        return self._sampled[:n]
+
     def check_status(self) -> None:
-        """Raise if a kernel reported a bad token id or position since the last check."""
+        """Raise if a kernel reported bad input or an expired wait since the last check."""
         code = int(self._status.item())
         if code:
             self._status.zero_()
-            raise StepError(f"a kernel reported bad input (status {code}: bit0 token id, bit1 position)")
+            raise StepError(f"a kernel reported bad input (status {code}: bit0 token id or NaN logits, bit1 position)")
+        ops.check_kernel_status(self.device)

@@ -64,6 +64,7 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.version = 0      # bumped whenever a buffer moves; recorded graphs check it
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         key = (name, dtype)
@@ -72,6 +73,7 @@ class Workspace:
         if buf is None or buf.numel() < need:
             buf = torch.empty(max(need, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.version += 1
         return buf[:need].view(rows, cols)
 
     def reserve(self, name: str, numel: int, dtype: torch.dtype) -> None:

@@ -159,3 +159,136 @@ def test_gemm_tc_refuses_what_it_cannot_take():
     with pytest.raises(ops.UnsupportedShape):
         ops.gemm_tc(a, w, None, out)          # K = 60 is no multiple of 8
     assert not ops.tensor_core_gemm_supported(60, 16)
+
+
+# ---- attention over the paged cache ------------------------------------------------------------
+def _paged_case(dtype, H, Hkv, D, page_size, seqs, seed, spike=None):
+    """seqs: list of (tokens already cached, new tokens).  Builds q for the new tokens, dense
+    K/V per request, and a cache whose pages are handed out in a shuffled order; the cached
+    prefix is written directly, the new tokens' K/V through kv_append.  `spike`: (request,
+    key position): that key and every query of the request are scaled so that this one score
+    stands out among hundreds."""
+    from sandyrt_b200.csrc import ops
+
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    n_blocks = [-(-(b + n) // page_size) for b, n in seqs]
+    num_pages = sum(n_blocks) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    max_blocks = max(n_blocks) + 2
+    table = torch.full((len(seqs), max_blocks), -1, dtype=torch.int32)
+    arena = torch.full((num_pages, 2, Hkv, page_size, D), float("nan"), dtype=dtype)
+    dense_k, dense_v, qs, tok_seq, tok_pos, k_new, v_new = [], [], [], [], [], [], []
+    for s, (before, n) in enumerate(seqs):
+        L = before + n
+        k = torch.randn(L, Hkv, D, generator=g)
+        v = torch.randn(L, Hkv, D, generator=g)
+        q = torch.randn(n, H, D, generator=g)
+        if spike is not None and spike[0] == s:
+            k[spike[1]] *= 6.0
+            q = q.abs() * torch.sign(k[spike[1]]).repeat_interleave(H // Hkv, dim=0) * 1.5
+        k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+        dense_k.append(k); dense_v.append(v); qs.append(q)
+        for b in range(n_blocks[s]):
+            table[s, b] = perm.pop()
+        for p in range(before):
+            page = table[s, p // page_size]
+            arena[page, 0, :, p % page_size] = k[p]
+            arena[page, 1, :, p % page_size] = v[p]
+        tok_seq += [s] * n
+        tok_pos += list(range(before, L))
+        k_new.append(k[before:]); v_new.append(v[before:])
+    arena = arena.to(DEV)
+    kc, vc = arena[:, 0], arena[:, 1]
+    table = table.to(DEV)
+    tok_seq = torch.tensor(tok_seq, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(tok_pos, dtype=torch.int32, device=DEV)
+    kv_src = torch.cat([torch.cat(k_new).reshape(-1, Hkv * D), torch.cat(v_new).reshape(-1, Hkv * D)], dim=1).to(DEV)
+    ops.kv_append(kv_src[:, :Hkv * D], kv_src[:, Hkv * D:], kc, vc, table, tok_seq, tok_pos)
+    q_all = torch.cat(qs).reshape(-1, H * D).to(DEV)
+    return dict(q=q_all, kc=kc, vc=vc, table=table, tok_seq=tok_seq, tok_pos=tok_pos,
+                dense_k=dense_k, dense_v=dense_v, qs=qs, seqs=seqs)
+
+
+def _attention_want(case, H, Hkv, D, scale, window):
+    outs = []
+    for s, (before, n) in enumerate(case["seqs"]):
+        k, v, q = case["dense_k"][s].double(), case["dense_v"][s].double(), case["qs"][s].double()
+        for i in range(n):
+            pos = before + i
+            lo = max(0, pos + 1 - window) if window else 0
+            row = []
+            for h in range(H):
+                kh = h // (H // Hkv)
+                sc = (k[lo:pos + 1, kh] @ q[i, h]) * scale
+                p = torch.softmax(sc, dim=0)
+                row.append(p @ v[lo:pos + 1, kh])
+            outs.append(torch.cat(row))
+    return torch.stack(outs)
+
+
+ATT_TOL = {torch.float32: 2e-5, torch.bfloat16: 1.2e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,D,page_size,window", [(4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (5, 5, 48, 8, 0),
+                                                     (6, 2, 64, 16, 0), (5, 1, 80, 4, 0), (4, 2, 128, 32, 0),
+                                                     (3, 3, 32, 16, 20), (6, 3, 64, 8, 37), (2, 1, 256, 16, 0)])
+def test_paged_attention_general(dtype, H, Hkv, D, page_size, window):
+    from sandyrt_b200.csrc import ops
+
+    seqs = [(0, 33), (40, 1), (17, 24), (0, 1), (63, 2), (100, 1)]
+    case = _paged_case(dtype, H, Hkv, D, page_size, seqs, seed=D + H)
+    out = torch.full_like(case["q"], float("nan"))
+    scale = 0.7 / math.sqrt(D)
+    ops.paged_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"], out,
+                        n_heads=H, scale=scale, window=window)
+    ops.check_kernel_status(DEV)
+    want = _attention_want(case, H, Hkv, D, scale, window)
+    assert (out.double().cpu() - want).abs().max().item() < ATT_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,D,page_size,window", [(4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (12, 12, 64, 16, 0),
+                                                     (6, 2, 64, 8, 0), (4, 1, 128, 32, 0), (5, 5, 64, 16, 100)])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+def test_decode_attention_split_kv(dtype, H, Hkv, D, page_size, window, splits):
+    """Single tokens over contexts of 1 to 700 keys, the keys split over several blocks."""
+    from sandyrt_b200.csrc import ops
+
+    seqs = [(699, 1), (0, 1), (63, 1), (64, 1), (300, 1), (15, 1), (128, 1)]
+    case = _paged_case(dtype, H, Hkv, D, page_size, seqs, seed=D + splits)
+    out = torch.full_like(case["q"], float("nan"))
+    scale = 1.0 / math.sqrt(D)
+    T = case["q"].shape[0]
+    scratch = torch.full((T * H * splits * (D + 2),), float("nan"), dtype=torch.float32, device=DEV)
+    ops.decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"], out,
+                         n_heads=H, scale=scale, window=window, num_splits=splits, scratch=scratch)
+    ops.check_kernel_status(DEV)
+    want = _attention_want(case, H, Hkv, D, scale, window)
+    assert (out.double().cpu() - want).abs().max().item() < ATT_TOL[dtype]
+
+
+@pytest.mark.parametrize("kernel", ["general", "decode"])
+def test_one_far_key_among_hundreds(kernel):
+    """Scale one query/key pair so that a single score dominates: a kernel that dropped or
+    misplaced that key (a page's edge, a split's edge) returns a visibly different output."""
+    from sandyrt_b200.csrc import ops
+
+    H = Hkv = 2
+    D = 64
+    for far in (0, 15, 16, 255, 256, 399, 511, 640):
+        seqs = [(641, 1), (5, 1)]
+        case = _paged_case(torch.float32, H, Hkv, D, 16, seqs, seed=far, spike=(0, far))
+        out = torch.full_like(case["q"], float("nan"))
+        if kernel == "general":
+            ops.paged_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"],
+                                out, n_heads=H, scale=0.125)
+        else:
+            scratch = torch.empty(2 * H * 7 * (D + 2), dtype=torch.float32, device=DEV)
+            ops.decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"],
+                                 out, n_heads=H, scale=0.125, num_splits=7, scratch=scratch)
+        got = out[0].view(H, D).cpu()
+        v_far = case["dense_v"][0][far]
+        assert (got - v_far).abs().max().item() < 1e-3, f"far key {far}: output is not that key's value"
+        want = _attention_want(case, H, Hkv, D, 0.125, 0)
+        assert (out.double().cpu() - want).abs().max().item() < 2e-5
