@@ -89,12 +89,14 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
 #pragma unroll
     for (int i = 0; i < VEC; i++) o[i] = 0.0f;
 
-    for (int j0 = begin + group; j0 < end; j0 += GROUPS * UNROLL) {
+    // The trip count is the same for every lane of a warp (the shuffles below need the whole
+    // warp): `base` is warp-uniform, and a group whose key lies past `end` just sits the round out.
+    for (int base = begin + warp * KPW; base < end; base += GROUPS * UNROLL) {
         float kf[UNROLL][VEC], vf[UNROLL][VEC];
         bool ok[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
-            const int j = j0 + u * GROUPS;
+            const int j = base + g + u * GROUPS;
             ok[u] = j < end;
             if (ok[u]) {
                 const int b = j / page_size;

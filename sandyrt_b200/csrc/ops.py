@@ -235,9 +235,41 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
         LAUNCHES += 1
 
 
+def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out, *, n_heads: int,
+                      max_q_len: int, scale: float, window: int = 0) -> None:
+    """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).
+    q_start: int32 [S+1] first new token of each request; kv_before: int32 [S]."""
+    _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out)
+    hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
+    if q.dtype != torch.bfloat16 or d % 16 != 0 or d > 128:
+        raise UnsupportedShape(f"prefill_attention: bfloat16 and head sizes 16..128 only, got {q.dtype}, {d}")
+    if n_heads % hkv != 0:
+        raise UnsupportedShape(f"attention: {n_heads} heads do not divide into {hkv} key/value heads")
+    if q.shape[1] != n_heads * d or out.shape != q.shape or q.stride(1) != 1 or out.stride(1) != 1 \
+            or q.dtype != k_cache.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
+    _i32(block_table, "block_table"); _i32(q_start, "q_start"); _i32(kv_before, "kv_before")
+    S = kv_before.numel()
+    if q_start.numel() != S + 1 or block_table.shape[0] != S:
+        raise KernelError("prefill_attention: q_start, kv_before and block_table disagree on the requests")
+    lib = load_library("attention_prefill")
+    code = lib.sandy_prefill_attention(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+                                       ctypes.c_longlong(page_stride), _p(block_table),
+                                       ctypes.c_int(block_table.shape[1]), _p(q_start), _p(kv_before), _p(out),
+                                       ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len),
+                                       ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps),
+                                       ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_pages),
+                                       _p(kernel_status(q.device)), _stream())
+    _check(code, f"prefill_attention(H={n_heads},Hkv={hkv},D={d})")
+
+
 def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale: float, window: int = 0) -> None:
     """Attention of a step's tokens over the cache: picks the kernel for the step's shape."""
     d = k_cache.shape[3]
+    if ctx.max_q_len > 1 and q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 128:
+        prefill_attention(q, k_cache, v_cache, block_table, ctx.q_start, ctx.kv_before, out, n_heads=n_heads,
+                          max_q_len=ctx.max_q_len, scale=scale, window=window)
+        return
     if ctx.max_q_len == 1 and d in _DECODE_HEAD_DIMS.get(q.dtype, ()):
         max_kv = block_table.shape[1] * k_cache.shape[2]
         splits = decode_splits(ctx.n_tokens, n_heads, max_kv)

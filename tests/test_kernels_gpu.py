@@ -292,3 +292,45 @@ def test_one_far_key_among_hundreds(kernel):
         assert (got - v_far).abs().max().item() < 1e-3, f"far key {far}: output is not that key's value"
         want = _attention_want(case, H, Hkv, D, 0.125, 0)
         assert (out.double().cpu() - want).abs().max().item() < 2e-5
+
+
+@pytest.mark.parametrize("H,Hkv,D,page_size,window", [(4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (5, 5, 48, 8, 0),
+                                                     (12, 12, 64, 16, 0), (6, 2, 64, 16, 0), (5, 1, 80, 4, 0),
+                                                     (4, 2, 128, 32, 0), (3, 3, 32, 16, 20), (6, 3, 64, 8, 70),
+                                                     (2, 2, 96, 16, 0), (2, 1, 112, 16, 0)])
+def test_prefill_attention_tensor_cores(H, Hkv, D, page_size, window):
+    """Portions that start at 0 and in the middle of a prompt, of 1 to 200 tokens, beside
+    single tokens; tile edges (63/64/65), page edges, windows."""
+    from sandyrt_b200.csrc import ops
+
+    seqs = [(0, 200), (40, 1), (17, 64), (0, 1), (63, 65), (100, 2), (0, 63), (129, 130)]
+    case = _paged_case(torch.bfloat16, H, Hkv, D, page_size, seqs, seed=D + H)
+    out = torch.full_like(case["q"], float("nan"))
+    scale = 1.0 / math.sqrt(D)
+    lens = [n for _, n in seqs]
+    q_start = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
+    kv_before = torch.tensor([b for b, _ in seqs], dtype=torch.int32, device=DEV)
+    ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
+                          max_q_len=max(lens), scale=scale, window=window)
+    ops.check_kernel_status(DEV)
+    want = _attention_want(case, H, Hkv, D, scale, window)
+    assert not torch.isnan(out).any()
+    assert (out.double().cpu() - want).abs().max().item() < 2e-2
+
+
+def test_prefill_attention_far_key():
+    from sandyrt_b200.csrc import ops
+
+    H = Hkv = 2
+    D = 64
+    for far in (0, 63, 64, 127, 300, 511, 512):
+        seqs = [(520, 90), (5, 3)]
+        case = _paged_case(torch.bfloat16, H, Hkv, D, 16, seqs, seed=far, spike=(0, far))
+        out = torch.full_like(case["q"], float("nan"))
+        q_start = torch.tensor([0, 90, 93], dtype=torch.int32, device=DEV)
+        kv_before = torch.tensor([520, 5], dtype=torch.int32, device=DEV)
+        ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
+                              max_q_len=90, scale=0.125)
+        v_far = case["dense_v"][0][far].float()
+        got = out[:90].view(90, H, D).float().cpu()
+        assert (got - v_far).abs().max().item() < 3e-2, f"far key {far}"
