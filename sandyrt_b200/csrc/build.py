@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "norm": [],
     "gemm_simt": [],
     "gemm_tc": [],
+    "gemm_skinny": [],
     "attention": [],
     "attention_decode": [],
     "attention_prefill": [],

@@ -26,7 +26,7 @@ constexpr int THREADS = (BM / TM) * (BN / TN);  // 256
 template <typename TA, typename TW, typename TC, bool W_OUT_IN>
 __global__ void __launch_bounds__(THREADS)
 gemm_simt_kernel(const TA* __restrict__ a, const TW* __restrict__ w, const TW* __restrict__ bias,
-                 const float* __restrict__ residual, TC* __restrict__ out,
+                 const float* residual, TC* out,
                  int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];

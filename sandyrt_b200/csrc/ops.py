@@ -16,6 +16,8 @@ import torch
 from .build import load_library
 
 F32, BF16 = 0, 1
+# Up to this many rows a bfloat16 product goes to the weight-streaming kernel, above it to tcgen05.
+SKINNY_MAX_ROWS = 64
 ACT_CODES = {None: 0, "none": 0, "gelu_new": 1, "gelu_tanh": 1, "gelu": 2, "gelu_erf": 2}
 
 
@@ -361,3 +363,34 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> Non
                              ctypes.c_int(out.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(out)),
                              ctypes.c_int(tile_n), _p(kernel_status(a.device)), _stream())
     _check(code, f"gemm_tc(M={M},N={N},K={K})")
+
+
+def gemm_skinny(a, w, bias, out, *, act=None, residual=None) -> None:
+    """out = act(a @ w.T + bias) + residual for up to 64 rows (a decode step), weight-streaming.
+    Same operand rules as gemm_tc."""
+    _cuda(a, w, bias, out, residual)
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise UnsupportedShape("gemm_skinny takes bfloat16 operands")
+    if M > 64:
+        raise UnsupportedShape(f"gemm_skinny takes at most 64 rows, got {M}")
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_skinny: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_skinny: innermost stride must be 1")
+    if K % 8 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        raise UnsupportedShape(f"gemm_skinny: K={K} and the row pitches must be multiples of 8 elements, "
+                               "operands 16-byte aligned")
+    if residual is not None and (residual.dtype != torch.float32 or residual.stride(1) != 1
+                                 or tuple(residual.shape) != (M, N)):
+        raise KernelError("gemm_skinny: residual must be float32 [M, N]")
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N):
+        raise KernelError("gemm_skinny: bias must be bfloat16 [N]")
+    lib = load_library("gemm_skinny")
+    code = lib.sandy_gemm_skinny(_p(a), _p(w), _p(bias), _p(residual), _p(out), ctypes.c_int(M), ctypes.c_int(N),
+                                 ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
+                                 ctypes.c_int(0 if residual is None else residual.stride(0)),
+                                 ctypes.c_int(out.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(out)),
+                                 _stream())
+    _check(code, f"gemm_skinny(M={M},N={N},K={K})")

@@ -61,6 +61,9 @@ class Linear:
                  residual: Optional[torch.Tensor] = None) -> None:
         """out = act(a @ W + b) + residual.  `out` may be `residual` itself."""
         if self.use_tensor_cores:
-            ops.gemm_tc(a, self.weight, self.bias, out, act=act, residual=residual)
+            if a.shape[0] <= ops.SKINNY_MAX_ROWS:
+                ops.gemm_skinny(a, self.weight, self.bias, out, act=act, residual=residual)
+            else:
+                ops.gemm_tc(a, self.weight, self.bias, out, act=act, residual=residual)
         else:
             ops.gemm_simt(a, self.weight, self.bias, out, w_out_in=self.w_out_in, act=act, residual=residual)

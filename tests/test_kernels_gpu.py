@@ -334,3 +334,28 @@ def test_prefill_attention_far_key():
         v_far = case["dense_v"][0][far].float()
         got = out[:90].view(90, H, D).float().cpu()
         assert (got - v_far).abs().max().item() < 3e-2, f"far key {far}"
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(64, 64), (2304, 768), (777, 240), (50257, 64), (96, 320), (1000, 96), (13, 8)])
+def test_gemm_skinny(M, N, K):
+    """The decode-step product at 1..64 rows, odd N, K that is no multiple of its 32-wide chunks."""
+    from sandyrt_b200.csrc import ops
+
+    a = _rand((M, K), torch.bfloat16, 1)
+    w_nk = _rand((N, K), torch.bfloat16, 2, scale=0.1)
+    bias = _rand((N,), torch.bfloat16, 3)
+    res = _rand((M, N), torch.float32, 4)
+    for act, use_res, out_dtype, use_bias in ((None, False, torch.bfloat16, True), ("gelu_new", False, torch.bfloat16, True),
+                                              ("gelu", False, torch.bfloat16, True), (None, True, torch.float32, True),
+                                              (None, False, torch.float32, False)):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        ops.gemm_skinny(a, w_nk, bias if use_bias else None, out, act=act, residual=res if use_res else None)
+        want = _gemm_want(a, w_nk.t(), bias if use_bias else None, act, res if use_res else None)
+        tol = 1e-2 if out_dtype == torch.bfloat16 else 2e-5
+        err = (out.double() - want).abs().max().item()
+        assert err < tol * (1 + want.abs().max().item()), (act, use_res, out_dtype, err)
+    # in place on the residual
+    x = res.clone()
+    ops.gemm_skinny(a, w_nk, None, x, residual=x)
+    assert (x.double() - (res.double() + a.double() @ w_nk.double().t())).abs().max().item() < 1e-4
