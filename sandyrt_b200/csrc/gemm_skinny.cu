@@ -5,8 +5,8 @@
 //
 // a: [M, K] bfloat16 (M <= 64), w: [N, K] bfloat16 (K contiguous), as in gemm_tc.cu.  With so
 // few rows the product is bound by streaming w from HBM, and a 128-row tensor-memory tile
-// would leave most SMs idle; here every block owns just 8 output columns and its four warps
-// split K between them, so a 768 x 768 weight is read by 96 blocks at once.  The arithmetic
+// would leave most SMs idle; here every block owns just 8 output columns and its eight warps
+// split K between them, so a 768 x 768 weight is read by 96 blocks of eight warps at once.  The arithmetic
 // runs on the warp-level tensor-core instruction (mma.sync m16n8k16: 16 tokens x 8 columns),
 // which is far more than this bandwidth-bound product needs.
 //
@@ -16,14 +16,14 @@
 // order its terms are paired, the same assignment of k to fragment slots is used for both
 // operands and no shuffle through shared memory is needed.
 //
-// The four warps' partial sums are added in a fixed order (warp 0..3), so a token's result
+// The warps' partial sums are added in a fixed order (warp 0, 1, ...), so a token's result
 // does not depend on what else is in the batch beyond which 16-row group it falls in (rows of
 // other tokens never enter its dot products).
 #include "epilogue.cuh"
 
 namespace {
 
-constexpr int WARPS = 4;
+constexpr int WARPS = 8;
 constexpr int COLS = 8;          // output columns per block
 constexpr int KCHUNK = 32;       // k covered by one 16-byte load of every lane
 constexpr int UNROLL = 4;
@@ -73,12 +73,22 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
     const bf16* wrow = w + (size_t)(n_ok ? n : 0) * ldw;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
+    // The weight pieces of the next round are requested before the current round is
+    // multiplied, so a warp always has two rounds of loads in flight.
+    uint4 wn[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) {
+        const int k = (c_begin + u) * KCHUNK + t * 8;
+        wn[u] = (n_ok && c_begin + u < c_end && k < K) ? ldg16_stream(wrow + k) : zero;
+    }
     for (int c0 = c_begin; c0 < c_end; c0 += UNROLL) {
         uint4 wv[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
-            const int k = (c0 + u) * KCHUNK + t * 8;
-            wv[u] = (n_ok && c0 + u < c_end && k < K) ? ldg16_stream(wrow + k) : zero;
+            wv[u] = wn[u];
+            const int cn = c0 + UNROLL + u;
+            const int k = cn * KCHUNK + t * 8;
+            wn[u] = (n_ok && cn < c_end && k < K) ? ldg16_stream(wrow + k) : zero;
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
