@@ -113,7 +113,7 @@ class Engine:
         self._staging = _Staging(self.device, 1 << (cap - 1).bit_length())
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._sampled = torch.zeros(max(max_requests, 1), dtype=torch.int32, device=self.device)
-        self.use_cuda_graphs = use_cuda_graphs
+        self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
         self._graphs: Dict[Tuple, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._seen: Dict[Tuple, int] = {}
         self.steps_run = 0

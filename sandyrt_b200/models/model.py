@@ -100,6 +100,11 @@ class Model:
         return specs
 
     @property
+    def graph_safe(self) -> bool:
+        """Whether every part may be recorded in a CUDA graph (see Part.graph_safe)."""
+        return all(getattr(part, "graph_safe", True) for part, _ in self._parts())
+
+    @property
     def max_positions(self) -> Optional[int]:
         return self.position.max_positions
 

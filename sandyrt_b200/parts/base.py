@@ -108,6 +108,12 @@ class StepContext:
 class Part:
     """Base of every part: tensor requests and binding."""
 
+    # A part whose `forward` only launches kernels that read the step's device arrays may be
+    # recorded in a CUDA graph and replayed.  A part that decides anything from the step's
+    # host-side lists (ctx.host_*) must set this to False; the engine then runs every step of
+    # a model that holds such a part without graphs.
+    graph_safe = True
+
     def __init__(self, spec: PartSpec):
         self.spec = spec
         self.params: Dict[str, Any] = dict(spec.params)

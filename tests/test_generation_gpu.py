@@ -1,0 +1,158 @@
+"""Generation through the Python entry point against the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import TINY
+from plain_gpt2 import generate_greedy, kept_set_and_cdf
+
+pytestmark = pytest.mark.gpu
+
+
+def _prompts(name, lengths, seed):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, TINY[name]["vocab_size"], size=n).tolist() for n in lengths]
+
+
+def _llm(model_dir, dtype="float32", **kw):
+    from sandyrt_b200.engine.llm import LLM
+
+    kw.setdefault("cache_tokens", 2048)
+    kw.setdefault("max_live", 8)
+    return LLM(model_dir, dtype=dtype, **kw)
+
+
+def test_greedy_tiny_a_matches_plain(model_dirs, plain_models):
+    """tiny A: 3 prompts of 5/17/33 tokens, 16 greedy tokens each, float32."""
+    llm = _llm(model_dirs["A"])
+    prompts = _prompts("A", [5, 17, 33], seed=21)
+    plain = plain_models("A", "f32")
+    want = [generate_greedy(plain, p, 16) for p in prompts]
+    got = llm.generate(prompts, max_tokens=16)
+    for g, (w_ids, w_reason), p in zip(got, want, prompts):
+        assert g.output_ids == w_ids and g.finish_reason == w_reason == "length"
+        assert g.prompt_tokens == len(p) and g.completion_tokens == 16
+        assert g.decode_tokens_per_second > 0 and g.prefill_tokens_per_second > 0
+
+
+def test_greedy_bfloat16_follows_the_plain_bfloat16_model(model_dirs, plain_models):
+    """bfloat16 may break a near-tie differently; wherever the plain bfloat16 model's top two
+    logits are clearly apart, the engine must pick the same token."""
+    llm = _llm(model_dirs["B"], dtype="bfloat16")
+    plain = plain_models("B", "bf16")
+    for p in _prompts("B", [9, 40], seed=22):
+        out = llm.generate(p, max_tokens=12)[0].output_ids
+        ids = list(p)
+        for tok in out:
+            l = plain.logits(ids)[-1]
+            top2 = np.sort(l)[-2:]
+            if top2[1] - top2[0] > 2e-2:
+                assert tok == int(np.argmax(l))
+            ids.append(tok)
+
+
+def test_temperature_sampling_tiny_b_chunked_prefill(model_dirs, plain_models):
+    """tiny B: prompts of 1/40/64/100 tokens, prompt portions of 24 tokens, 20 tokens each at
+    temperature 0.8 with a fixed seed.  Every drawn token must be the one the plain model's
+    distribution assigns to the request's uniform number for that step."""
+    from sandyrt_b200.sampling.sampler import uniform_for
+
+    llm = _llm(model_dirs["B"], prefill_chunk_tokens=24, max_step_tokens=64)
+    plain = plain_models("B", "f32")
+    prompts = _prompts("B", [1, 40, 64, 100], seed=23)
+    res = llm.generate(prompts, max_tokens=20, temperature=0.8, seed=1234)
+    again = _llm(model_dirs["B"], prefill_chunk_tokens=7, max_step_tokens=33).generate(
+        prompts, max_tokens=20, temperature=0.8, seed=1234)
+    for i, (p, r, r2) in enumerate(zip(prompts, res, again)):
+        assert len(r.output_ids) == 20 and r.finish_reason == "length"
+        assert r.output_ids == r2.output_ids          # same seed, other portion sizes: same tokens
+        ids = list(p)
+        for step, tok in enumerate(r.output_ids):
+            kept, cdf = kept_set_and_cdf(plain.logits(ids)[-1], 0.8)
+            u = uniform_for(1234 + i, step)
+            j = int(np.where(kept == tok)[0][0])
+            lo = cdf[j - 1] if j else 0.0
+            assert lo - 1e-4 <= u <= cdf[j] + 1e-4, f"request {i} step {step}: token {tok} does not match u={u}"
+            ids.append(tok)
+    assert len({tuple(r.output_ids) for r in res}) == 4        # different seeds per request
+
+
+def test_stop_tokens_and_zero_max_tokens(model_dirs, plain_models):
+    llm = _llm(model_dirs["A"])
+    plain = plain_models("A", "f32")
+    p = _prompts("A", [12], seed=24)[0]
+    free_run, _ = generate_greedy(plain, p, 10)
+    stop = free_run[4]
+    first = free_run.index(stop)
+    r = llm.generate(p, max_tokens=10, stop_token_ids=[stop])[0]
+    assert r.output_ids == free_run[:first + 1] and r.finish_reason == "stop"   # the stop token is part of the output
+    r0 = llm.generate(p, max_tokens=0)[0]
+    assert r0.output_ids == [] and r0.finish_reason == "length" and r0.completion_tokens == 0
+
+
+def test_long_decoding_to_the_last_position(model_dirs, plain_models):
+    """Decode until the model's positions run out (128 for tiny A): many pages, every position."""
+    llm = _llm(model_dirs["A"])
+    plain = plain_models("A", "f32")
+    p = _prompts("A", [3], seed=25)[0]
+    r = llm.generate(p, max_tokens=500)[0]
+    want, reason = generate_greedy(plain, p, 500)
+    assert r.finish_reason == reason == "length"
+    assert len(p) + len(r.output_ids) == TINY["A"]["n_positions"] + 1 or len(r.output_ids) == len(want)
+    n = min(len(want), len(r.output_ids))
+    assert r.output_ids[:n] == want[:n] and n >= 120
+
+
+def test_first_tokens_of_a_sequence(model_dirs, plain_models):
+    """A prompt of a single token, and the very first logits of a sequence."""
+    from sandyrt_b200.engine.step import StepEntry
+
+    llm = _llm(model_dirs["B"])
+    plain = plain_models("B", "f32")
+    for tok in (0, 999, 417):
+        out = llm.engine.step([StepEntry(f"one-{tok}", [tok], [0])]).cpu().numpy()
+        llm.engine.release(f"one-{tok}")
+        np.testing.assert_allclose(out[0], plain.logits([tok])[0], atol=2e-5, rtol=1e-4)
+    r = llm.generate([417], max_tokens=5)[0]
+    assert r.output_ids == generate_greedy(plain, [417], 5)[0]
+
+
+def test_preemption_does_not_change_the_output(model_dirs):
+    """With a cache too small for all requests at once some are preempted and recomputed; the
+    tokens must be the same as with plenty of room."""
+    prompts = _prompts("A", [30, 28, 26, 31], seed=26)
+    roomy = _llm(model_dirs["A"], cache_tokens=4096).generate(prompts, max_tokens=40)
+    tight_llm = _llm(model_dirs["A"], cache_tokens=160, page_size=16)     # 10 pages for 4 x ~70 tokens
+    tight = tight_llm.generate(prompts, max_tokens=40)
+    assert tight_llm.scheduler.stats["preemptions"] > 0
+    assert [r.output_ids for r in tight] == [r.output_ids for r in roomy]
+    assert sum(r.preemptions for r in tight) == tight_llm.scheduler.stats["preemptions"]
+    tight_llm.engine.cache.alloc.check()
+    assert tight_llm.engine.cache.alloc.free_pages() == 10
+
+
+def test_refusals_through_the_entry_point(model_dirs):
+    from sandyrt_b200.engine.scheduler import RequestRefused
+
+    llm = _llm(model_dirs["A"])
+    with pytest.raises(RequestRefused, match="empty"):
+        llm.generate([[]], max_tokens=4)
+    with pytest.raises(RequestRefused, match="vocabulary"):
+        llm.generate([5, 512], max_tokens=4)
+    with pytest.raises(RequestRefused, match="positions"):
+        llm.generate(list(range(129)), max_tokens=4)
+    with pytest.raises(ValueError, match="top_p"):
+        llm.generate([1, 2], max_tokens=4, top_p=0.0)
+
+
+def test_on_token_callback_can_cancel(model_dirs):
+    llm = _llm(model_dirs["A"])
+    seen = []
+
+    def cb(index, token):
+        seen.append((index, token))
+        return len(seen) < 3
+
+    r = llm.generate([5, 6, 7], max_tokens=50, on_token=cb)[0]
+    assert r.finish_reason == "cancelled" and len(r.output_ids) == 3 == len(seen)
+    assert llm.engine.cache.alloc.free_slots() == 8      # everything was given back

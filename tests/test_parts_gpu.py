@@ -1,0 +1,334 @@
+"""Each part alone against the plain implementation's function for it, and a toy model made
+of parts the framework has never seen: a mixer with a state of its own, different mixers in
+different layers, a layer that runs twice and a layer that reads another layer's cache."""
+import dataclasses
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _np(t):
+    return t.detach().float().cpu().numpy()
+
+
+def _spec(kind, params, names):
+    from sandyrt_b200.models.spec import PartSpec
+
+    return PartSpec(kind, params, {n: n for n in names})
+
+
+def _random_bind(part, seed, dtype):
+    from sandyrt_b200.weights.random_init import random_tensors
+
+    tensors = random_tensors(part.requests(), seed, torch.float32)
+    part.bind(tensors, DEV, dtype)
+    return {k: v.numpy() for k, v in tensors.items()}
+
+
+def _ctx(cache_specs, seqs, dtype, page_size=8):
+    """A hand-made StepContext for parts run outside a model.  seqs: [(kv_before, q_len)]."""
+    from sandyrt_b200.cache.manager import CacheManager
+    from sandyrt_b200.parts.base import StepContext, Workspace
+
+    cm = CacheManager(cache_specs, page_size=page_size, max_tokens=512, max_requests=8, device=DEV, dtype=dtype)
+    cm.device_caches.poison()
+    pos, seq, qs = [], [], [0]
+    for s, (before, n) in enumerate(seqs):
+        cm.admit(s)
+        cm.alloc.reserve(s, before + n)
+        pos += list(range(before, before + n)); seq += [s] * n; qs.append(qs[-1] + n)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    max_blocks = max(len(cm.alloc.block_list(s, 0)) for s in range(len(seqs))) if cm.layout.groups else 1
+    tables = {}
+    for g in cm.layout.groups:
+        t = torch.full((len(seqs), max_blocks), -1, dtype=torch.int32)
+        for s in range(len(seqs)):
+            bl = cm.alloc.block_list(s, g.index)
+            t[s, :len(bl)] = torch.tensor(bl, dtype=torch.int32)
+        tables[g.index] = t.to(DEV)
+    T = len(pos)
+    return StepContext(
+        n_tokens=T, n_seqs=len(seqs), token_ids=i32([0] * T), positions=i32(pos), token_seq=i32(seq),
+        seq_slots=i32([cm.alloc.slot(s) for s in range(len(seqs))]), q_start=i32(qs),
+        kv_before=i32([b for b, _ in seqs]), logit_rows=i32([]), block_tables=tables, compute_dtype=dtype,
+        workspace=Workspace(DEV), caches=cm.device_caches, host_q_lens=[n for _, n in seqs],
+        host_kv_before=[b for b, _ in seqs], host_slots=[cm.alloc.slot(s) for s in range(len(seqs))],
+        max_q_len=max(n for _, n in seqs), max_kv_len=max(b + n for b, n in seqs)), cm
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
+def test_layernorm_part(dtype, tol):
+    from sandyrt_b200.registry import get_part
+
+    part = get_part("norm", "layernorm")(_spec("layernorm", {"width": 96, "eps": 1e-6}, ["weight", "bias"]))
+    w = _random_bind(part, 1, dtype)
+    x = torch.randn(11, 96, device=DEV) * 2 + 0.5
+    out = torch.empty(11, 96, dtype=dtype, device=DEV)
+    part.forward(None, x, out)
+    want = plain.layer_norm(_np(x), w["weight"], w["bias"], 1e-6)
+    assert np.abs(_np(out) - want).max() < tol
+
+
+def test_embedding_with_learned_positions():
+    from sandyrt_b200.parts.base import StepContext, Workspace
+    from sandyrt_b200.parts.embedding import TokenEmbedding
+    from sandyrt_b200.registry import get_part
+
+    emb = TokenEmbedding(_spec("token_embedding", {"vocab_size": 77, "width": 48}, ["weight"]))
+    pos = get_part("position", "learned_absolute")(_spec("learned_absolute", {"width": 48, "max_positions": 20}, ["weight"]))
+    we, wp = _random_bind(emb, 1, torch.float32), _random_bind(pos, 2, torch.float32)
+    ctx, _ = _ctx([], [(3, 4), (0, 2)], torch.float32)
+    ids = [5, 76, 0, 13, 9, 9]
+    ctx.token_ids = torch.tensor(ids, dtype=torch.int32, device=DEV)
+    ctx.position = pos
+    x = torch.empty(6, 48, device=DEV)
+    emb.forward(ctx, x, None)
+    want = plain.embedding(ids, we["weight"]) + plain.embedding([3, 4, 5, 6, 0, 1], wp["weight"])
+    np.testing.assert_allclose(_np(x), want, atol=1e-7)
+    assert pos.max_positions == 20
+    assert get_part("position", "none")(_spec("none", {}, [])).max_positions is None
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("activation,layout", [("gelu_new", "in_out"), ("gelu", "out_in")])
+def test_dense_mlp_part(dtype, tol, activation, layout):
+    from sandyrt_b200.registry import get_part
+
+    part = get_part("feed_forward", "dense_mlp")(_spec(
+        "dense_mlp", {"width": 64, "inner": 200, "activation": activation, "weight_layout": layout},
+        ["up.weight", "up.bias", "down.weight", "down.bias"]))
+    w = _random_bind(part, 3, dtype)
+    ctx, _ = _ctx([], [(0, 9)], dtype)
+    h = torch.randn(9, 64, device=DEV).to(dtype)
+    x = torch.randn(9, 64, device=DEV)
+    x0 = _np(x).copy()
+    part.forward(ctx, h, x)
+    store = "bf16" if dtype == torch.bfloat16 else "f32"
+    rnd = plain.round_bf16 if store == "bf16" else (lambda a: a)
+    wt = (lambda a: a) if layout == "in_out" else (lambda a: a.T)
+    u = plain.linear_in_out(_np(h), rnd(wt(w["up.weight"])), rnd(w["up.bias"]))
+    g = rnd(plain.gelu_new(u) if activation == "gelu_new" else plain.gelu_erf(u))
+    want = x0 + plain.linear_in_out(g, rnd(wt(w["down.weight"])), rnd(w["down.bias"]))
+    assert np.abs(_np(x) - want).max() < tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [(4, 4, 16, None), (6, 2, 32, None), (3, 3, 32, 9)])
+def test_attention_part_whole_then_in_portions(dtype, tol, n_heads, n_kv_heads, head_dim, window):
+    """The attention part over its own cache: a sequence in one step equals the same
+    sequence in two portions plus single tokens (grouped heads and a window included)."""
+    from sandyrt_b200.parts.base import LayerCallCtx
+    from sandyrt_b200.registry import get_part
+
+    width = 80
+    part = get_part("mixer", "causal_attention")(_spec(
+        "causal_attention", {"width": width, "n_heads": n_heads, "n_kv_heads": n_kv_heads, "head_dim": head_dim,
+                             "scale": 0.3, "window": window, "weight_layout": "out_in"},
+        ["qkv.weight", "qkv.bias", "out.weight", "out.bias"]))
+    w = _random_bind(part, 4, dtype)
+    T = 37
+    h_all = (torch.randn(T, width, device=DEV) * 1.5).to(dtype)
+
+    def run(cuts):
+        outs, before = [], 0
+        ctx, cm = None, None
+        for n in cuts:
+            if ctx is None:
+                ctx, cm = _ctx([part.cache_spec()], [(0, n)], dtype)
+            else:
+                cm.alloc.commit(0, before)
+                cm.alloc.reserve(0, before + n)
+                bl = cm.alloc.block_list(0, 0)
+                table = torch.full((1, max(len(bl), 1)), -1, dtype=torch.int32)
+                table[0, :len(bl)] = torch.tensor(bl, dtype=torch.int32)
+                ctx.block_tables = {0: table.to(DEV)}
+                ctx.n_tokens = n
+                ctx.positions = torch.arange(before, before + n, dtype=torch.int32, device=DEV)
+                ctx.token_seq = torch.zeros(n, dtype=torch.int32, device=DEV)
+                ctx.q_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+                ctx.kv_before = torch.tensor([before], dtype=torch.int32, device=DEV)
+                ctx.host_q_lens, ctx.host_kv_before, ctx.max_q_len, ctx.max_kv_len = [n], [before], n, before + n
+            x = torch.zeros(n, width, device=DEV)
+            part.forward(ctx, h_all[before:before + n].contiguous(), x, LayerCallCtx(0, True))
+            outs.append(_np(x))
+            before += n
+        return np.concatenate(outs)
+
+    whole = run([T])
+    parts = run([20, 2, 1, 1, 13])
+    assert np.abs(whole - parts).max() < tol
+    # against the plain functions
+    rnd = plain.round_bf16 if dtype == torch.bfloat16 else (lambda a: a)
+    qkv = rnd(plain.linear_in_out(_np(h_all), rnd(w["qkv.weight"].T), rnd(w["qkv.bias"])))
+    qc, kc = n_heads * head_dim, n_kv_heads * head_dim
+    split = lambda t, nh: t.reshape(T, nh, head_dim).transpose(1, 0, 2)
+    o = plain.causal_attention(split(qkv[:, :qc], n_heads), split(qkv[:, qc:qc + kc], n_kv_heads),
+                               split(qkv[:, qc + kc:], n_kv_heads), 0.3, window or 0)
+    o = rnd(o.transpose(1, 0, 2).reshape(T, qc))
+    want = plain.linear_in_out(o, rnd(w["out.weight"].T), rnd(w["out.bias"]))
+    assert np.abs(whole - want).max() < tol
+
+
+# ---- a toy architecture assembled from registered parts ---------------------------------------
+def _register_toy():
+    """Registers, from outside the framework: a mixer with per-request state of fixed size
+    (an exponential moving average of its input), and an architecture that mixes it with
+    attention layers, runs one layer twice and lets one layer read another layer's cache."""
+    from sandyrt_b200.config.base import ModelConfig
+    from sandyrt_b200.models.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
+    from sandyrt_b200.parts.base import Mixer, StateSpec
+    from sandyrt_b200.registry import register_architecture, register_part
+    from sandyrt_b200.weights.loader import TensorRequest
+
+    class EmaMixer(Mixer):
+        """s_t = decay * s_{t-1} + h_t (per channel);  x_t += s_t * gain.  State: s, float32 [width]."""
+        graph_safe = False        # it plans its work from the step's host-side lists
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.width, self.decay = int(self.params["width"]), float(self.params["decay"])
+
+        def requests(self):
+            return {"gain": TensorRequest((self.width,), init="gamma")}
+
+        def bind(self, tensors, device, dtype):
+            self.gain = tensors["gain"].to(device=device, dtype=torch.float32)
+
+        def cache_spec(self):
+            return StateSpec((self.width,))
+
+        def forward(self, ctx, h, x, call):
+            state = ctx.caches.state(call.cache)
+            t0 = 0
+            for n, slot in zip(ctx.host_q_lens, ctx.host_slots):
+                s = state[slot].clone()
+                for i in range(n):
+                    s = self.decay * s + h[t0 + i].float()
+                    x[t0 + i] += s * self.gain
+                state[slot] = s
+                t0 += n
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture = "ToyMixedModel"
+        width: int = 0
+        vocab_size: int = 0
+        decay: float = 0.9
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(width=raw["width"], vocab_size=raw["vocab_size"], decay=raw["decay"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "width": self.width, "vocab_size": self.vocab_size,
+                    "decay": self.decay}
+
+        def validate(self):
+            assert self.width % 16 == 0
+
+    def describe(cfg):
+        E = cfg.width
+        norm = lambda n: PartSpec("layernorm", {"width": E, "eps": 1e-5}, {"weight": n + ".g", "bias": n + ".b"})
+        mlp = lambda p: PartSpec("dense_mlp", {"width": E, "inner": 2 * E, "activation": "gelu_new",
+                                               "weight_layout": "out_in"},
+                                 {"up.weight": p + "up.w", "up.bias": p + "up.b", "down.weight": p + "dn.w",
+                                  "down.bias": p + "dn.b"})
+        attn = lambda p: PartSpec("causal_attention", {"width": E, "n_heads": 2, "n_kv_heads": 1, "head_dim": E // 2,
+                                                       "scale": 1 / math.sqrt(E // 2), "weight_layout": "out_in"},
+                                  {"qkv.weight": p + "qkv.w", "qkv.bias": p + "qkv.b", "out.weight": p + "o.w",
+                                   "out.bias": p + "o.b"})
+        layers = [
+            LayerSpec("pre_norm", PartSpec("toy_ema", {"width": E, "decay": cfg.decay}, {"gain": "l0.gain"}),
+                      mlp("l0."), {"mixer": norm("l0.n1"), "feed_forward": norm("l0.n2")}),
+            LayerSpec("pre_norm", attn("l1."), mlp("l1."), {"mixer": norm("l1.n1"), "feed_forward": norm("l1.n2")}),
+            LayerSpec("pre_norm", attn("l2."), mlp("l2."), {"mixer": norm("l2.n1"), "feed_forward": norm("l2.n2")}),
+        ]
+        schedule = [LayerCall(0, 0), LayerCall(1, 1), LayerCall(1, 2),          # layer 1 runs twice, two caches
+                    LayerCall(2, 1, write_cache=False)]                          # layer 2 reads layer 1's first cache
+        return ModelSpec(architecture=cfg.architecture, width=E, vocab_size=cfg.vocab_size, max_positions=None,
+                         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "width": E}, {"weight": "emb"}),
+                         position=PartSpec("none", {}, {}), layers=layers, schedule=schedule,
+                         final_norm=norm("nf"), head=PartSpec("output_head", {"vocab_size": cfg.vocab_size, "width": E,
+                                                                              "tied": True}, {}))
+
+    register_part("mixer", "toy_ema", EmaMixer)
+    register_architecture("ToyMixedModel", ToyConfig, describe)
+    return ToyConfig
+
+
+def _toy_plain_logits(w, ids, decay, E):
+    """The toy model, whole sequence, written with the plain implementation's functions."""
+    T = len(ids)
+    x = plain.embedding(ids, w["emb"])
+    ln = lambda x, n: plain.layer_norm(x, w[n + ".g"], w[n + ".b"], 1e-5)
+    lin = lambda h, p: plain.linear_in_out(h, w[p + "w"].T, w[p + "b"])
+    mlp = lambda x, p: x + lin(plain.gelu_new(lin(ln(x, p + "n2"), p + "up.")), p + "dn.")
+    D = E // 2
+    split = lambda t, nh: t.reshape(T, nh, D).transpose(1, 0, 2)
+
+    def attn(x, p, kv=None):
+        qkv = lin(ln(x, p + "n1"), p + "qkv.")
+        q = split(qkv[:, :E], 2)
+        k, v = (split(qkv[:, E:E + D], 1), split(qkv[:, E + D:], 1)) if kv is None else kv
+        o = plain.causal_attention(q, k, v, 1 / math.sqrt(D)).transpose(1, 0, 2).reshape(T, E)
+        return x + lin(o, p + "o."), (k, v)
+
+    h = ln(x, "l0.n1")
+    s = np.zeros(E, np.float32)
+    y = np.zeros_like(x)
+    for t in range(T):
+        s = decay * s + h[t]
+        y[t] = s * w["l0.gain"]
+    x = mlp(x + y, "l0.")
+    x, kv1 = attn(x, "l1."); x = mlp(x, "l1.")
+    x, _ = attn(x, "l1."); x = mlp(x, "l1.")
+    x, _ = attn(x, "l2.", kv=kv1); x = mlp(x, "l2.")
+    return plain.layer_norm(x, w["nf.g"], w["nf.b"], 1e-5) @ w["emb"].T
+
+
+def test_toy_model_with_stateful_mixer_registers_builds_and_steps(tmp_path):
+    from sandyrt_b200.engine.step import Engine, StepEntry
+    from sandyrt_b200.models.model import load_model
+    from sandyrt_b200.weights.random_init import write_random_model
+
+    ToyConfig = _register_toy()
+    cfg = ToyConfig(width=32, vocab_size=90, decay=0.8)
+    d = write_random_model(cfg, str(tmp_path / "toy"), seed=3, dtype=torch.float32)
+    assert json.load(open(os.path.join(d, "config.json")))["architectures"] == ["ToyMixedModel"]
+    model = load_model(d, device=DEV, dtype=torch.float32)          # chosen by config.json through the registry
+    assert not model.graph_safe
+    eng = Engine(model, max_tokens=256, page_size=8, max_requests=3)
+    layout = eng.cache.layout
+    assert list(layout.state_of_cache) == [0] and len(layout.groups) == 1 and layout.groups[0].caches == [1, 2]
+    w = plain.read_safetensors(os.path.join(d, "model.safetensors"))
+    rng = np.random.default_rng(0)
+    seqs = {name: rng.integers(0, 90, size=n).tolist() for name, n in (("a", 23), ("b", 9), ("c", 31), ("d", 14))}
+    want = {k: _toy_plain_logits(w, v, 0.8, 32) for k, v in seqs.items()}
+    got = {k: [] for k in seqs}
+    # a and b start together; c joins when b has ended and takes over b's slot and pages
+    plan = [
+        [("a", 10), ("b", 9)], [("a", 1)], [("a", 2), ("c", 16)], [("c", 1), ("a", 10)], [("c", 14)],
+        [("d", 14)],
+    ]
+    fed = {k: 0 for k in seqs}
+    for step in plan:
+        entries = [StepEntry(k, seqs[k][fed[k]:fed[k] + n], list(range(n))) for k, n in step]
+        out = eng.step(entries).cpu().numpy()
+        r = 0
+        for k, n in step:
+            got[k].append(out[r:r + n].copy()); r += n; fed[k] += n
+            if fed[k] == len(seqs[k]):
+                eng.release(k)
+        eng.cache.alloc.check()
+    for k in seqs:
+        np.testing.assert_allclose(np.concatenate(got[k]), want[k], atol=3e-5, rtol=1e-4, err_msg=f"sequence {k}")
+    assert eng.cache.alloc.free_slots() == 3
