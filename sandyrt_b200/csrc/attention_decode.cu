@@ -245,3 +245,73 @@ SANDY_API int sandy_decode_attention(const void* q, int ld_q, const void* k_cach
 #undef CASE
     return SANDY_ERR_UNSUPPORTED;
 }
+
+// ---- the entry point that allocates nothing ------------------------------------------------
+// See attention_decode_static.h for who needs it, its limit and its rules.
+#include "attention_decode_static.h"
+
+namespace {
+
+// The scratch of sandy_decode_attention_static().  In host code this name is only a handle
+// for cudaGetSymbolAddress: it is NOT a device address and must never be passed to a kernel.
+static __device__ __align__(256) float g_decode_static_scratch[SANDY_DECODE_STATIC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+
+// Device address of the array on the current device, looked up once per device.
+float* static_scratch_address(int* error) {
+    static float* address[MAX_DEVICES] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        *error = SANDY_ERR_STATIC_SETUP;
+        return nullptr;
+    }
+    if (address[dev] == nullptr) {
+        float* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_decode_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            *error = SANDY_ERR_STATIC_SETUP;
+            return nullptr;
+        }
+        address[dev] = p;
+    }
+    return address[dev];
+}
+
+}  // namespace
+
+SANDY_API long long sandy_decode_attention_static_capacity(void) {
+    return (long long)SANDY_DECODE_STATIC_SCRATCH_FLOATS;
+}
+
+SANDY_API const char* sandy_decode_attention_static_strerror(int code) {
+    switch (code) {
+        case SANDY_OK: return "ok";
+        case SANDY_ERR_UNSUPPORTED: return "sizes or dtypes this kernel does not take";
+        case SANDY_ERR_ARGUMENT: return "a null pointer or an impossible size";
+        case SANDY_ERR_STATIC_SCRATCH:
+            return "the shape needs more scratch than the static array holds "
+                   "(n_tokens * n_heads * num_splits * (head_dim + 2) floats > 1048576): "
+                   "use fewer splits or sandy_decode_attention() with a buffer of your own";
+        case SANDY_ERR_STATIC_SETUP: return "the device address of the static scratch array could not be obtained";
+        default: return code > 0 ? "a CUDA error (the value is a cudaError_t)" : "unknown code";
+    }
+}
+
+SANDY_API int sandy_decode_attention_static(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                            long long page_stride, const int* block_table, int max_blocks,
+                                            const int* token_seq, const int* positions, void* out, int ld_out,
+                                            int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                            float scale, int window, int num_splits, int num_pages, int dtype,
+                                            int* status, cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (n_tokens < 0 || n_heads <= 0 || head_dim <= 0 || num_splits < 1) return SANDY_ERR_ARGUMENT;
+    const long long need = sandy_decode_attention_scratch_floats(n_tokens, n_heads, head_dim, num_splits);
+    if (need > (long long)SANDY_DECODE_STATIC_SCRATCH_FLOATS) return SANDY_ERR_STATIC_SCRATCH;
+    int error = SANDY_OK;
+    float* scratch = static_scratch_address(&error);     // first call on a device: the one-time look-up
+    if (scratch == nullptr) return error;
+    return sandy_decode_attention(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq,
+                                  positions, out, ld_out, scratch, n_tokens, n_heads, n_kv_heads, head_dim,
+                                  page_size, scale, window, num_splits, num_pages, dtype, status, stream);
+}
