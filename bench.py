@@ -121,33 +121,68 @@ def make_model(n_layer: int, seed: int = 0):
     return model, cfg
 
 
-def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, timed_with_events=True):
-    """Prefill `batch` prompts, then time `steps` decode steps after `warmup` untimed ones.
-    Returns (ms per step on the device, ms per step on the wall clock, mean context length)."""
-    import torch
-
-    rids = [llm.add_request(rng.integers(0, vocab, size=prompt_len).tolist(), max_tokens=steps + warmup + 1)
+def _start_decoding(llm, batch, prompt_len, max_tokens, warmup, rng, vocab):
+    """Add `batch` requests, run their prompts and `warmup` decode steps through the entry point."""
+    rids = [llm.add_request(rng.integers(0, vocab, size=prompt_len).tolist(), max_tokens=max_tokens)
             for _ in range(batch)]
     while any(len(llm._requests[r].output) == 0 for r in rids):       # prefill
         llm.step()
     for _ in range(warmup):
         llm.step()
+    return rids
+
+
+def _drop(llm, rids):
+    for r in rids:
+        if r in llm.engine.cache.alloc:
+            llm.engine.release(r)
+        llm.scheduler.running = [q for q in llm.scheduler.running if q.rid != r]
+        llm.forget(r)
+
+
+def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, want_e2e=True):
+    """Times `steps` decode steps of `batch` requests after `warmup` untimed ones, twice:
+
+    device: the engine's step (index arrays copied from pinned memory, model, sampler), steps
+            issued back to back with no read-back in between, timed with CUDA events;
+    e2e:    the same number of steps through the entry point (LLM.step: scheduler, host token
+            ids in, drawn tokens read back to the host every step), timed on the wall clock.
+
+    Returns (device ms/step, e2e ms/step, mean context length, launches per step)."""
+    import torch
+
+    from sandyrt_b200.engine.step import SampleRow, StepEntry
+
+    e2e_ms = None
+    if want_e2e:
+        rids = _start_decoding(llm, batch, prompt_len, steps + warmup + 1, warmup, rng, vocab)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            llm.step()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+        _drop(llm, rids)
+
+    rids = _start_decoding(llm, batch, prompt_len, steps + warmup + 8, warmup, rng, vocab)
+    engine = llm.engine
+    ctx0 = sum(engine.length(r) for r in rids) / batch
+    rows = [SampleRow() for _ in rids]
+    tokens = rng.integers(0, vocab, size=(steps + 2, batch))
+    for i in range(2):                                   # the direct loop's own shape: warm it
+        engine.step([StepEntry(r, [int(tokens[i, k])], [0]) for k, r in enumerate(rids)], sampling=rows)
     torch.cuda.synchronize()
-    ctx0 = sum(llm._requests[r].n_tokens for r in rids) / batch
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
     e0.record()
-    for _ in range(steps):
-        llm.step()
+    for i in range(steps):
+        engine.step([StepEntry(r, [int(tokens[i + 2, k])], [0]) for k, r in enumerate(rids)], sampling=rows)
     e1.record()
     torch.cuda.synchronize()
-    wall_ms = (time.perf_counter() - t0) * 1e3
-    dev_ms = e0.elapsed_time(e1)
-    ctx1 = sum(llm._requests[r].n_tokens for r in rids) / batch
-    for r in rids:
-        llm.abort(r)
-        llm.forget(r)
-    return dev_ms / steps, wall_ms / steps, 0.5 * (ctx0 + ctx1)
+    dev_ms = e0.elapsed_time(e1) / steps
+    ctx1 = sum(engine.length(r) for r in rids) / batch
+    launches = engine.last_launches
+    _drop(llm, rids)
+    return dev_ms, e2e_ms, 0.5 * (ctx0 + ctx1), launches
 
 
 def main() -> int:
@@ -189,9 +224,9 @@ def main() -> int:
     # The same loop gives the end-to-end number: every llm.step() packs the step's host token
     # ids into pinned memory, copies them to the device, runs the model and the sampler and
     # reads the drawn tokens back to the host before the next step is planned.
-    dev_ms, wall_ms, mean_ctx = decode_run(llm, args.batch, args.prompt_len, args.steps, args.warmup, rng, vocab)
+    dev_ms, wall_ms, mean_ctx, launches_per_step = decode_run(llm, args.batch, args.prompt_len, args.steps,
+                                                              args.warmup, rng, vocab)
     value = args.batch / (dev_ms / 1e3)
-    launches_per_step = engine.last_launches
     e2e_value = args.batch / (wall_ms / 1e3)
     weight_bytes = model.weight_bytes()
     kv_bytes = engine.cache.kv_bytes_per_token() * args.batch * mean_ctx
@@ -222,7 +257,8 @@ def main() -> int:
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            d_ms, _, _ = decode_run(llm, b, args.prompt_len, min(args.steps, 128), args.warmup, rng, vocab)
+            d_ms, _, _, _ = decode_run(llm, b, args.prompt_len, min(args.steps, 128), args.warmup, rng, vocab,
+                                       want_e2e=False)
             points[f"decode_b{b}"] = b / (d_ms / 1e3)
 
     clock_info = clocks.stop()

@@ -20,12 +20,22 @@
 //
 // Head sizes: D * sizeof(T) / 16 must divide 32 (D = 16, 32, 64, 128, and 256 in bfloat16).
 // Other head sizes are served by the general kernel in attention.cu.
+//
+// Merging the splits.  With up to 8 splits the blocks of one (token, head) pair are launched
+// as one thread-block cluster and merge through distributed shared memory: no scratch, no
+// second kernel (sandy_decode_attention_cluster).  The scratch form with its merge kernel
+// remains for more splits and for callers that want it (sandy_decode_attention).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
 constexpr int WARPS = 4;
 constexpr int UNROLL = 4;
+constexpr int MAX_CLUSTER_SPLITS = 8;      // the portable cluster size
 
 template <typename T, int VEC>
 __device__ __forceinline__ void load_vec(const T* p, float (&f)[VEC]);
@@ -65,7 +75,10 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
 
     __shared__ float sm_m[GROUPS], sm_l[GROUPS];
     __shared__ float sm_o[GROUPS][D];
+    __shared__ float cl_o[D], cl_ml[2];        // this block's partial state, read by its cluster
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int split = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane / LPK, sub = lane % LPK;
@@ -158,6 +171,13 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
         }
         if (num_splits == 1) {
             out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+        } else if (partial_o == nullptr) {
+            // cluster mode: the splits of this (token, head) are the blocks of one cluster
+            cl_o[d] = O;
+            if (d == 0) {
+                cl_ml[0] = M;
+                cl_ml[1] = L;
+            }
         } else {
             const size_t slot = ((size_t)t * n_heads + h) * num_splits + split;
             partial_o[slot * D + d] = O;
@@ -167,11 +187,37 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
             }
         }
     }
+    if (num_splits > 1 && partial_o == nullptr) {
+        // Merge through distributed shared memory: every block leaves its partial state in its
+        // own shared memory, the cluster's first block reads them all (fixed order: split 0, 1, ..)
+        // and writes the result; nobody leaves before that block is done reading.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (cluster.block_rank() == 0) {
+            float M = -INFINITY;
+            for (int r = 0; r < num_splits; r++) M = fmaxf(M, cluster.map_shared_rank(cl_ml, r)[0]);
+            for (int d = threadIdx.x; d < D; d += WARPS * 32) {
+                float L = 0.0f, O = 0.0f;
+                if (M > -INFINITY) {
+                    for (int r = 0; r < num_splits; r++) {
+                        const float* rml = cluster.map_shared_rank(cl_ml, r);
+                        const float w = expf(rml[0] - M);
+                        L = fmaf(rml[1], w, L);
+                        O = fmaf(cluster.map_shared_rank(cl_o, r)[d], w, O);
+                    }
+                }
+                out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+            }
+        }
+        cluster.sync();
+    }
 }
 
 template <typename T, int D>
 __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                     T* __restrict__ out, int ld_out, int n_heads, int num_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int h = blockIdx.x, t = blockIdx.y;
     const size_t base = ((size_t)t * n_heads + h) * num_splits;
     float M = -INFINITY;
@@ -197,18 +243,72 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + (size_t)n_tokens * n_heads * num_splits * D : nullptr;
     dim3 grid(num_splits, n_heads, n_tokens);
-    decode_attention_kernel<T, D><<<grid, WARPS * 32, 0, stream>>>(
-        (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, token_seq,
-        positions, (T*)out, ld_out, partial_o, partial_ml, n_heads, n_kv_heads, page_size, scale, window,
-        num_splits, num_pages, status);
-    int code = sandy_launch_status();
+    int code = sandy_launch(decode_attention_kernel<T, D>, grid, dim3(WARPS * 32), 0, stream, (const T*)q, ld_q,
+                            (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, token_seq,
+                            positions, (T*)out, ld_out, partial_o, partial_ml, n_heads, n_kv_heads, page_size, scale,
+                            window, num_splits, num_pages, status);
     if (code != 0 || num_splits == 1) return code;
-    merge_splits_kernel<T, D><<<dim3(n_heads, n_tokens), D < 32 ? 32 : (D > 256 ? 256 : D), 0, stream>>>(
-        partial_o, partial_ml, (T*)out, ld_out, n_heads, num_splits);
-    return sandy_launch_status();
+    return sandy_launch(merge_splits_kernel<T, D>, dim3(n_heads, n_tokens), dim3(D < 32 ? 32 : (D > 256 ? 256 : D)), 0,
+                        stream, (const float*)partial_o, (const float*)partial_ml, (T*)out, ld_out, n_heads, num_splits);
+}
+
+// Cluster form: grid (splits, heads, tokens), clusters of (splits, 1, 1).
+template <typename T, int D>
+int launch_cluster(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                   const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
+                   int ld_out, int n_tokens, int n_heads, int n_kv_heads, int page_size, float scale, int window,
+                   int num_splits, int num_pages, int* status, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_splits, n_heads, n_tokens);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = num_splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = sandy_pdl_enabled() ? 2 : 1;
+    const cudaError_t e = cudaLaunchKernelEx(
+        &cfg, decode_attention_kernel<T, D>, (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride,
+        block_table, max_blocks, token_seq, positions, (T*)out, ld_out, (float*)nullptr, (float*)nullptr, n_heads,
+        n_kv_heads, page_size, scale, window, num_splits, num_pages, status);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 }  // namespace
+
+// The cluster form: 2 <= num_splits <= 8, no scratch.  Other arguments as sandy_decode_attention.
+SANDY_API int sandy_decode_attention_cluster(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                             long long page_stride, const int* block_table, int max_blocks,
+                                             const int* token_seq, const int* positions, void* out, int ld_out,
+                                             int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                             float scale, int window, int num_splits, int num_pages, int dtype,
+                                             int* status, cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out) return SANDY_ERR_ARGUMENT;
+    if (num_splits < 2 || num_splits > MAX_CLUSTER_SPLITS) return SANDY_ERR_UNSUPPORTED;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0) return SANDY_ERR_UNSUPPORTED;
+    if (n_heads > 65535 || n_tokens > 65535) return SANDY_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
+        (reinterpret_cast<uintptr_t>(v_cache) & 15))
+        return SANDY_ERR_UNSUPPORTED;
+    const int esz = dtype == SANDY_F32 ? 4 : 2;
+    if ((ld_q * esz) % 16 != 0 || (page_stride * esz) % 16 != 0) return SANDY_ERR_UNSUPPORTED;
+#define CASE(DT, TT, DD)                                                                                        \
+    if (dtype == DT && head_dim == DD)                                                                          \
+        return launch_cluster<TT, DD>(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq, \
+                                      positions, out, ld_out, n_tokens, n_heads, n_kv_heads, page_size, scale,  \
+                                      window, num_splits, num_pages, status, stream)
+    CASE(SANDY_BF16, bf16, 16); CASE(SANDY_BF16, bf16, 32); CASE(SANDY_BF16, bf16, 64);
+    CASE(SANDY_BF16, bf16, 128); CASE(SANDY_BF16, bf16, 256);
+    CASE(SANDY_F32, float, 16); CASE(SANDY_F32, float, 32); CASE(SANDY_F32, float, 64); CASE(SANDY_F32, float, 128);
+#undef CASE
+    return SANDY_ERR_UNSUPPORTED;
+}
 
 // Floats of scratch the split kernel needs for this shape (0 when num_splits == 1).
 SANDY_API long long sandy_decode_attention_scratch_floats(int n_tokens, int n_heads, int head_dim, int num_splits) {

@@ -75,3 +75,46 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 static inline int sandy_launch_status() {
     return (int)cudaGetLastError();
 }
+
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A decode step is a chain of ~70 short kernels, each only a few microseconds long, so what
+// a kernel costs is mostly getting started: launch latency and the first trip to memory.
+// Launched with the programmatic-serialization attribute, a kernel may start while its
+// predecessor in the stream is still running (as soon as every block of the predecessor has
+// called pdl_launch_dependents() or exited).  It must then call pdl_wait() before it reads
+// anything an earlier kernel wrote or writes anything an earlier kernel may still read;
+// pdl_wait() returns when the predecessor has completed and its writes are visible.  What may
+// go before pdl_wait() is work on data no kernel writes: index arithmetic and, above all, the
+// first loads of the weights.  Both calls do nothing in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+#include <utility>
+
+// SANDYRT_PDL=0 turns the attribute off (every kernel then waits for its predecessor to end).
+static inline bool sandy_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = std::getenv("SANDYRT_PDL");
+        enabled = (e && e[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int sandy_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = sandy_pdl_enabled() ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}

@@ -15,6 +15,8 @@ __global__ void embed_pos_kernel(const int* __restrict__ ids, const int* __restr
                                  const TT* __restrict__ wte, const TT* __restrict__ wpe,
                                  TO* __restrict__ out, int width, int vocab, int n_pos,
                                  int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const int p = wpe ? pos[t] : 0;
@@ -42,12 +44,11 @@ SANDY_API int sandy_embed_pos(const int* ids, const int* pos, const void* wte, c
     if (!ids || !wte || !out || width <= 0) return SANDY_ERR_ARGUMENT;
     const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
 #define LAUNCH(TT, TO)                                                                          \
-    embed_pos_kernel<TT, TO><<<n_tokens, threads, 0, stream>>>(                                 \
-        ids, pos, (const TT*)wte, (const TT*)wpe, (TO*)out, width, vocab, n_pos, status)
+    return sandy_launch(embed_pos_kernel<TT, TO>, dim3(n_tokens), dim3(threads), 0, stream, ids, pos,  \
+                        (const TT*)wte, (const TT*)wpe, (TO*)out, width, vocab, n_pos, status)
     if (table_dtype == SANDY_F32 && out_dtype == SANDY_F32) LAUNCH(float, float);
-    else if (table_dtype == SANDY_BF16 && out_dtype == SANDY_F32) LAUNCH(bf16, float);
-    else if (table_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) LAUNCH(bf16, bf16);
-    else return SANDY_ERR_UNSUPPORTED;
+    if (table_dtype == SANDY_BF16 && out_dtype == SANDY_F32) LAUNCH(bf16, float);
+    if (table_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) LAUNCH(bf16, bf16);
 #undef LAUNCH
-    return sandy_launch_status();
+    return SANDY_ERR_UNSUPPORTED;
 }

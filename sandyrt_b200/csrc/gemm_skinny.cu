@@ -1,24 +1,35 @@
 // bfloat16 matrix product for a few rows (a decode step: 1 to 64 tokens), shaped for
-// reading the weight once at memory speed rather than for arithmetic.
+// reading the weight once at memory speed rather than for arithmetic, with the work that
+// surrounds it in a decoder layer folded in:
 //
-//   out[m, n] = act( sum_k a[m, k] * w[n, k] + bias[n] ) + residual[m, n]
+//   a      = LayerNorm(x) (optional: the norm before the product runs inside this kernel)
+//   out    = act( a @ w^T + bias ) + residual
+//   cache  <- the key and value columns of out, written straight into the request's pages
+//             (optional: the product is the fused q/k/v projection)
 //
-// a: [M, K] bfloat16 (M <= 64), w: [N, K] bfloat16 (K contiguous), as in gemm_tc.cu.  With so
-// few rows the product is bound by streaming w from HBM, and a 128-row tensor-memory tile
-// would leave most SMs idle; here every block owns just 8 output columns and its eight warps
-// split K between them, so a 768 x 768 weight is read by 96 blocks of eight warps at once.  The arithmetic
-// runs on the warp-level tensor-core instruction (mma.sync m16n8k16: 16 tokens x 8 columns),
-// which is far more than this bandwidth-bound product needs.
+// a: [M, K] bfloat16 (M <= 64), or x: [M, K] float with gamma/beta when the norm is fused;
+// w: [N, K] bfloat16 (K contiguous), as in gemm_tc.cu.  With so few rows the product is bound
+// by streaming w from HBM, and a 128-row tensor-memory tile would leave most SMs idle; here
+// every block owns just 8 output columns and its eight warps split K between them, so a
+// 768 x 768 weight is read by 96 blocks of eight warps at once.  The arithmetic runs on the
+// warp-level tensor-core instruction (mma.sync m16n8k16: 16 tokens x 8 columns), which is far
+// more than this bandwidth-bound product needs.
 //
-// Each lane reads the weight and the activations in 16-byte pieces straight from global
-// memory (the activations are small and stay in L1/L2).  The 8 consecutive k of a 16-byte
-// piece are fed to two consecutive mma steps; since a dot product does not care in which
-// order its terms are paired, the same assignment of k to fragment slots is used for both
-// operands and no shuffle through shared memory is needed.
+// Each lane reads the weight in 16-byte pieces straight from global memory.  The 8
+// consecutive k of a piece are fed to two consecutive mma steps; since a dot product does not
+// care in which order its terms are paired, the same assignment of k to fragment slots is
+// used for both operands and no shuffle through shared memory is needed.  The first round of
+// weight loads is issued before anything else, so it overlaps the norm.
+//
+// Fused norm (src/core/TensorCalc.cpp:2048-2072 of the reference: mean, biased variance in
+// two passes, 1/sqrt(var + eps), gain and offset): every block normalises the M rows itself
+// (warp per row, the row held in registers, statistics in float) into shared memory as
+// bfloat16, the same rounding point as the stand-alone norm kernel.  This trades a launch for
+// re-reading x (M x K floats, from L2) in every block, which pays while M is small.
 //
 // The warps' partial sums are added in a fixed order (warp 0, 1, ...), so a token's result
-// does not depend on what else is in the batch beyond which 16-row group it falls in (rows of
-// other tokens never enter its dot products).
+// does not depend on what else is in the batch (rows of other tokens never enter its dot
+// products).
 #include "epilogue.cuh"
 
 namespace {
@@ -27,6 +38,8 @@ constexpr int WARPS = 8;
 constexpr int COLS = 8;          // output columns per block
 constexpr int KCHUNK = 32;       // k covered by one 16-byte load of every lane
 constexpr int UNROLL = 4;
+constexpr int XPAD = 32;         // elements of padding per shared-memory row (64 bytes: conflict-free 16-byte reads)
+constexpr int MAX_ROW_VEC = 16;  // float4 per lane a fused-norm row may take: K <= 2048
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -47,13 +60,37 @@ __device__ __forceinline__ uint4 ldg16_stream(const bf16* p) {
     return v;
 }
 
+// Where the key/value columns of a fused q/k/v product go (see attention.cu for the layout).
+struct KVWrite {
+    bf16* k_cache;
+    bf16* v_cache;
+    long long page_stride;
+    const int* block_table;
+    const int* token_seq;
+    const int* positions;
+    int max_blocks, q_cols, kv_cols, head_dim, page_size, num_pages;
+    int* status;
+};
+
+struct NormArgs {
+    const float* x;          // [M, K] float, row stride ldx
+    const bf16* gamma;       // [K]
+    const bf16* beta;        // [K] or null
+    int ldx;
+    float eps;
+};
+
 // MT: number of 16-row token tiles (M <= 16 * MT)
-template <int MT, typename TC>
+template <int MT, typename TC, bool FUSE_LN>
 __global__ void __launch_bounds__(WARPS * 32)
-gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const bf16* __restrict__ bias,
-                   const float* residual, TC* out, int M, int N, int K, int lda,
-                   int ldw, int ldr, int ldc, int act) {
+gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __restrict__ w,
+                   const bf16* __restrict__ bias, const float* residual, TC* out, int M, int N, int K, int lda,
+                   int ldw, int ldr, int ldc, int act, KVWrite kv) {
     __shared__ float partial[WARPS][MT * 16][COLS + 1];
+    extern __shared__ __align__(16) uint8_t xs_raw[];
+    bf16* xs = reinterpret_cast<bf16*>(xs_raw);          // [MT*16][K + XPAD], fused norm only
+    const int xs_ld = K + XPAD;
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * COLS;
@@ -74,13 +111,74 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
     // The weight pieces of the next round are requested before the current round is
-    // multiplied, so a warp always has two rounds of loads in flight.
+    // multiplied, so a warp always has two rounds of loads in flight; the first round goes out
+    // before the norm.
     uint4 wn[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; u++) {
         const int k = (c_begin + u) * KCHUNK + t * 8;
         wn[u] = (n_ok && c_begin + u < c_end && k < K) ? ldg16_stream(wrow + k) : zero;
     }
+
+    // Everything above touched only the weight, which no kernel writes.  From here on the
+    // activations are read: the kernels before this one must have finished.
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (FUSE_LN) {
+        // warp per row; the row lives in registers between the passes
+        for (int r = warp; r < MT * 16; r += WARPS) {
+            bf16* dst = xs + (size_t)r * xs_ld;
+            if (r >= M) {
+                for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = zero;
+                continue;
+            }
+            const float* xr = norm.x + (size_t)r * norm.ldx;
+            float4 v[MAX_ROW_VEC];
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < MAX_ROW_VEC; i++) {
+                const int k = (i * 32 + lane) * 4;
+                v[i] = k < K ? *reinterpret_cast<const float4*>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            }
+            const float mean = warp_sum(s) / (float)K;
+            float q = 0.0f;
+#pragma unroll
+            for (int i = 0; i < MAX_ROW_VEC; i++) {
+                const int k = (i * 32 + lane) * 4;
+                if (k < K) {
+                    const float cx = v[i].x - mean, cy = v[i].y - mean, cz = v[i].z - mean, cw = v[i].w - mean;
+                    q += (cx * cx + cy * cy) + (cz * cz + cw * cw);
+                }
+            }
+            const float inv = 1.0f / sqrtf(warp_sum(q) / (float)K + norm.eps);
+#pragma unroll
+            for (int i = 0; i < MAX_ROW_VEC; i++) {
+                const int k = (i * 32 + lane) * 4;
+                if (k < K) {
+                    const uint2 gm = *reinterpret_cast<const uint2*>(norm.gamma + k);
+                    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gm);
+                    const float2 g01 = __bfloat1622float2(gh[0]), g23 = __bfloat1622float2(gh[1]);
+                    float y0 = (v[i].x - mean) * inv * g01.x, y1 = (v[i].y - mean) * inv * g01.y;
+                    float y2 = (v[i].z - mean) * inv * g23.x, y3 = (v[i].w - mean) * inv * g23.y;
+                    if (norm.beta) {
+                        const uint2 bm = *reinterpret_cast<const uint2*>(norm.beta + k);
+                        const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bm);
+                        const float2 b01 = __bfloat1622float2(bh[0]), b23 = __bfloat1622float2(bh[1]);
+                        y0 += b01.x; y1 += b01.y; y2 += b23.x; y3 += b23.y;
+                    }
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(y0, y1), p1 = __floats2bfloat162_rn(y2, y3);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<uint32_t*>(&p0);
+                    pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                    *reinterpret_cast<uint2*>(dst + k) = pk;
+                }
+            }
+        }
+        __syncthreads();
+    }
+
     for (int c0 = c_begin; c0 < c_end; c0 += UNROLL) {
         uint4 wv[UNROLL];
 #pragma unroll
@@ -97,8 +195,14 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 const int r0 = mt * 16 + g, r1 = r0 + 8;
-                const uint4 x0 = (k_ok && r0 < M) ? ldg16(a + (size_t)r0 * lda + k) : zero;
-                const uint4 x1 = (k_ok && r1 < M) ? ldg16(a + (size_t)r1 * lda + k) : zero;
+                uint4 x0, x1;
+                if (FUSE_LN) {
+                    x0 = k_ok ? *reinterpret_cast<const uint4*>(xs + (size_t)r0 * xs_ld + k) : zero;
+                    x1 = k_ok ? *reinterpret_cast<const uint4*>(xs + (size_t)r1 * xs_ld + k) : zero;
+                } else {
+                    x0 = (k_ok && r0 < M) ? ldg16(a + (size_t)r0 * lda + k) : zero;
+                    x1 = (k_ok && r1 < M) ? ldg16(a + (size_t)r1 * lda + k) : zero;
+                }
                 // pieces .x .y feed the first mma step (slots 2t,2t+1 and 2t+8,2t+9), .z .w the second
                 mma_bf16(acc[mt], x0.x, x1.x, x0.y, x1.y, wv[u].x, wv[u].y);
                 mma_bf16(acc[mt], x0.z, x1.z, x0.w, x1.w, wv[u].z, wv[u].w);
@@ -125,34 +229,99 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
         v = apply_act(v, act);
         if (residual) v += residual[(size_t)m * ldr + col];
         out[(size_t)m * ldc + col] = from_f32<TC>(v);
+        if (kv.k_cache && col >= kv.q_cols) {
+            // a key or value element: straight into the request's page
+            const int c = col - kv.q_cols;
+            const bool is_v = c >= kv.kv_cols;
+            const int c2 = is_v ? c - kv.kv_cols : c;
+            const int head = c2 / kv.head_dim, d = c2 % kv.head_dim;
+            const int pos = kv.positions[m];
+            const int b = pos / kv.page_size;
+            const int page = (pos >= 0 && b < kv.max_blocks)
+                                 ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
+            if (page < 0 || page >= kv.num_pages) {
+                if (kv.status) atomicOr(kv.status, 8);
+            } else {
+                const size_t dst = (size_t)page * kv.page_stride +
+                                   ((size_t)head * kv.page_size + (pos % kv.page_size)) * kv.head_dim + d;
+                (is_v ? kv.v_cache : kv.k_cache)[dst] = __float2bfloat16_rn(v);
+            }
+        }
     }
 }
 
-template <int MT>
-int launch(const void* a, const void* w, const void* bias, const float* residual, void* out, int M, int N, int K,
-           int lda, int ldw, int ldr, int ldc, int act, int out_dtype, cudaStream_t stream) {
+template <int MT, bool FUSE_LN>
+int launch(const void* a, const NormArgs& norm, const void* w, const void* bias, const float* residual, void* out,
+           int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype, const KVWrite& kv,
+           cudaStream_t stream) {
     const unsigned blocks = (unsigned)((N + COLS - 1) / COLS);
-    if (out_dtype == SANDY_F32)
-        gemm_skinny_kernel<MT, float><<<blocks, WARPS * 32, 0, stream>>>(
-            (const bf16*)a, (const bf16*)w, (const bf16*)bias, residual, (float*)out, M, N, K, lda, ldw, ldr, ldc, act);
-    else
-        gemm_skinny_kernel<MT, bf16><<<blocks, WARPS * 32, 0, stream>>>(
-            (const bf16*)a, (const bf16*)w, (const bf16*)bias, residual, (bf16*)out, M, N, K, lda, ldw, ldr, ldc, act);
-    return sandy_launch_status();
+    const size_t smem = FUSE_LN ? (size_t)MT * 16 * (K + XPAD) * sizeof(bf16) : 0;
+    if (out_dtype == SANDY_F32) {
+        auto kern = gemm_skinny_kernel<MT, float, FUSE_LN>;
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return sandy_launch(kern, dim3(blocks), dim3(WARPS * 32), smem, stream, (const bf16*)a, norm, (const bf16*)w,
+                            (const bf16*)bias, residual, (float*)out, M, N, K, lda, ldw, ldr, ldc, act, kv);
+    } else {
+        auto kern = gemm_skinny_kernel<MT, bf16, FUSE_LN>;
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return sandy_launch(kern, dim3(blocks), dim3(WARPS * 32), smem, stream, (const bf16*)a, norm, (const bf16*)w,
+                            (const bf16*)bias, residual, (bf16*)out, M, N, K, lda, ldw, ldr, ldc, act, kv);
+    }
 }
 
 }  // namespace
 
+// Largest M and K the fused norm takes (the row is held in registers; the normalised rows
+// in shared memory).
+SANDY_API int sandy_gemm_skinny_norm_limits(int* max_rows, int* max_k) {
+    *max_rows = 16;
+    *max_k = MAX_ROW_VEC * 128;
+    return SANDY_OK;
+}
+
 // Arguments as sandy_gemm_tc; M <= 64; K, lda, ldw multiples of 8; a and w 16-byte aligned.
-SANDY_API int sandy_gemm_skinny(const void* a, const void* w, const void* bias, const float* residual, void* out,
+//
+// Fused norm: pass a = null and x (float [M, K], row stride ldx, 16-byte aligned, ldx % 4 == 0),
+// gamma, beta (bfloat16 [K], beta may be null), eps; M <= 16 and K <= 2048.
+// Key/value write: pass k_cache != null with the cache description of attention.cu; columns
+// [q_cols, q_cols + kv_cols) of the product are keys, the next kv_cols are values, and row m
+// belongs to position positions[m] of request token_seq[m].  out must be bfloat16 then.
+SANDY_API int sandy_gemm_skinny(const void* a, const float* x, int ldx, const void* gamma, const void* beta,
+                                float eps, const void* w, const void* bias, const float* residual, void* out,
                                 int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype,
+                                void* k_cache, void* v_cache, long long page_stride, const int* block_table,
+                                int max_blocks, const int* token_seq, const int* positions, int q_cols,
+                                int kv_cols, int head_dim, int page_size, int num_pages, int* status,
                                 cudaStream_t stream) {
     if (M == 0 || N == 0) return SANDY_OK;
-    if (!a || !w || !out || K <= 0) return SANDY_ERR_ARGUMENT;
-    if (M > 64 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return SANDY_ERR_UNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return SANDY_ERR_UNSUPPORTED;
+    const bool fuse = a == nullptr;
+    if ((!a && !x) || !w || !out || K <= 0) return SANDY_ERR_ARGUMENT;
+    if (M > 64 || K % 8 != 0 || ldw % 8 != 0) return SANDY_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(w) & 15) return SANDY_ERR_UNSUPPORTED;
     if (out_dtype != SANDY_F32 && out_dtype != SANDY_BF16) return SANDY_ERR_UNSUPPORTED;
-    if (M <= 16) return launch<1>(a, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, stream);
-    if (M <= 32) return launch<2>(a, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, stream);
-    return launch<4>(a, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, stream);
+    NormArgs norm{x, (const bf16*)gamma, (const bf16*)beta, ldx, eps};
+    if (fuse) {
+        if (!gamma || M > 16 || K > MAX_ROW_VEC * 128 || ldx % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) ||
+            (reinterpret_cast<uintptr_t>(gamma) & 7) || (beta && (reinterpret_cast<uintptr_t>(beta) & 7)))
+            return SANDY_ERR_UNSUPPORTED;
+    } else {
+        if (lda % 8 != 0 || (reinterpret_cast<uintptr_t>(a) & 15)) return SANDY_ERR_UNSUPPORTED;
+    }
+    KVWrite kv{(bf16*)k_cache, (bf16*)v_cache, page_stride, block_table, token_seq, positions,
+               max_blocks, q_cols, kv_cols, head_dim, page_size, num_pages, status};
+    if (k_cache) {
+        if (!v_cache || !block_table || !token_seq || !positions || out_dtype != SANDY_BF16 || head_dim <= 0 ||
+            kv_cols % head_dim != 0 || q_cols + 2 * kv_cols != N || page_size <= 0)
+            return SANDY_ERR_ARGUMENT;
+    }
+    if (fuse) return launch<1, true>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    if (M <= 16) return launch<1, false>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    if (M <= 32) return launch<2, false>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    return launch<4, false>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
 }

@@ -18,6 +18,8 @@ __global__ void layernorm_kernel(const TI* __restrict__ x, const TW* __restrict_
                                  const int* __restrict__ rows, int width, float eps) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     const TI* xr = x + src * width;
@@ -58,14 +60,13 @@ SANDY_API int sandy_layernorm(const void* x, const void* gamma, const void* beta
         if (smem > 48 * 1024)                                                                   \
             cudaFuncSetAttribute(layernorm_kernel<TI, TW, TO>,                                  \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        layernorm_kernel<TI, TW, TO><<<n_rows, threads, smem, stream>>>(                        \
-            (const TI*)x, (const TW*)gamma, (const TW*)beta, (TO*)out, rows, width, eps);       \
+        return sandy_launch(layernorm_kernel<TI, TW, TO>, dim3(n_rows), dim3(threads), smem, stream, \
+                            (const TI*)x, (const TW*)gamma, (const TW*)beta, (TO*)out, rows, width, eps); \
     } while (0)
     if (in_dtype == SANDY_F32 && w_dtype == SANDY_F32 && out_dtype == SANDY_F32) LAUNCH(float, float, float);
-    else if (in_dtype == SANDY_F32 && w_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) LAUNCH(float, bf16, bf16);
-    else if (in_dtype == SANDY_BF16 && w_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) LAUNCH(bf16, bf16, bf16);
-    else if (in_dtype == SANDY_F32 && w_dtype == SANDY_F32 && out_dtype == SANDY_BF16) LAUNCH(float, float, bf16);
-    else return SANDY_ERR_UNSUPPORTED;
+    if (in_dtype == SANDY_F32 && w_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) LAUNCH(float, bf16, bf16);
+    if (in_dtype == SANDY_BF16 && w_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) LAUNCH(bf16, bf16, bf16);
+    if (in_dtype == SANDY_F32 && w_dtype == SANDY_F32 && out_dtype == SANDY_BF16) LAUNCH(float, float, bf16);
 #undef LAUNCH
-    return sandy_launch_status();
+    return SANDY_ERR_UNSUPPORTED;
 }

@@ -205,9 +205,14 @@ def decode_splits(n_tokens: int, n_heads: int, max_kv: int) -> int:
     return max(1, min(want, cap, 32))
 
 
+CLUSTER_MAX_SPLITS = 8
+
+
 def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int,
-                     scale: float, window: int = 0, num_splits: int = 1, scratch=None) -> None:
-    """Split-KV attention of single tokens (head sizes 16/32/64/128, 256 in bfloat16)."""
+                     scale: float, window: int = 0, num_splits: int = 1, scratch=None, cluster: bool = False) -> None:
+    """Split-KV attention of single tokens (head sizes 16/32/64/128, 256 in bfloat16).  With
+    `cluster` (2..8 splits) the splits merge through distributed shared memory inside one
+    kernel; otherwise they go through `scratch` and a merge kernel."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, scratch)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -219,6 +224,18 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
             or q.dtype != k_cache.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
     _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
+    if cluster and num_splits > 1:
+        if num_splits > CLUSTER_MAX_SPLITS:
+            raise UnsupportedShape(f"decode_attention: a cluster holds at most {CLUSTER_MAX_SPLITS} splits")
+        lib = load_library("attention_decode")
+        code = lib.sandy_decode_attention_cluster(
+            _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride),
+            _p(block_table), ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
+            ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d),
+            ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_splits),
+            ctypes.c_int(num_pages), ctypes.c_int(_dt(q)), _p(kernel_status(q.device)), _stream())
+        _check(code, f"decode_attention_cluster(H={n_heads},Hkv={hkv},D={d},splits={num_splits})")
+        return
     need = T * n_heads * num_splits * (d + 2) if num_splits > 1 else 0
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need
                  or not scratch.is_contiguous()):
@@ -274,13 +291,9 @@ def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale
         return
     if ctx.max_q_len == 1 and d in _DECODE_HEAD_DIMS.get(q.dtype, ()):
         max_kv = block_table.shape[1] * k_cache.shape[2]
-        splits = decode_splits(ctx.n_tokens, n_heads, max_kv)
-        scratch = None
-        if splits > 1:
-            scratch = ctx.workspace.get("attention_splits", 1, ctx.n_tokens * n_heads * splits * (d + 2),
-                                        torch.float32).view(-1)
+        splits = min(decode_splits(ctx.n_tokens, n_heads, max_kv), CLUSTER_MAX_SPLITS)
         decode_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out, n_heads=n_heads,
-                         scale=scale, window=window, num_splits=splits, scratch=scratch)
+                         scale=scale, window=window, num_splits=splits, cluster=True)
         return
     paged_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out,
                     n_heads=n_heads, scale=scale, window=window)
@@ -365,21 +378,48 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> Non
     _check(code, f"gemm_tc(M={M},N={N},K={K})")
 
 
-def gemm_skinny(a, w, bias, out, *, act=None, residual=None) -> None:
+SKINNY_NORM_MAX_ROWS = 16
+SKINNY_NORM_MAX_K = 2048
+
+
+def skinny_norm_fusable(lazy, K: int) -> bool:
+    """Whether gemm_skinny can run this LazyNorm inside itself: a LayerNorm with bfloat16
+    gain/offset, at most 16 rows, K at most 2048 (the row is held in registers)."""
+    norm = lazy.norm
+    gamma = getattr(norm, "gamma", None)
+    return (getattr(norm, "fusable_kind", None) == "layernorm" and gamma is not None
+            and gamma.dtype == torch.bfloat16 and lazy.out_dtype == torch.bfloat16
+            and lazy.x.dtype == torch.float32 and lazy.x.shape[0] <= SKINNY_NORM_MAX_ROWS
+            and K <= SKINNY_NORM_MAX_K and lazy.x.stride(1) == 1 and lazy.x.stride(0) % 4 == 0
+            and lazy.x.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a, w, bias, out, *, act=None, residual=None, norm=None, kv=None) -> None:
     """out = act(a @ w.T + bias) + residual for up to 64 rows (a decode step), weight-streaming.
-    Same operand rules as gemm_tc."""
-    _cuda(a, w, bias, out, residual)
-    M, K = a.shape
+    Same operand rules as gemm_tc.  With `norm` (a LazyNorm that skinny_norm_fusable accepted)
+    `a` is None and the LayerNorm of norm.x runs inside the kernel.  With `kv` (a KVTarget) the
+    key and value columns of the product are also written into the cache pages."""
+    M, K = (norm.x.shape if norm is not None else a.shape)
     N = w.shape[0]
-    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+    x = gamma = beta = None
+    eps = 0.0
+    if norm is not None:
+        x, gamma, beta, eps = norm.x, norm.norm.gamma, norm.norm.beta, float(norm.norm.eps)
+        if not skinny_norm_fusable(norm, K):
+            raise UnsupportedShape("gemm_skinny: this norm cannot be fused")
+    elif a.dtype != torch.bfloat16:
+        raise UnsupportedShape("gemm_skinny takes bfloat16 operands")
+    _cuda(a, x, gamma, beta, w, bias, out, residual)
+    if w.dtype != torch.bfloat16:
         raise UnsupportedShape("gemm_skinny takes bfloat16 operands")
     if M > 64:
         raise UnsupportedShape(f"gemm_skinny takes at most 64 rows, got {M}")
     if w.shape[1] != K or tuple(out.shape) != (M, N):
-        raise KernelError(f"gemm_skinny: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm_skinny: shapes disagree: a {(M, K)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if (a is not None and a.stride(1) != 1) or w.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("gemm_skinny: innermost stride must be 1")
-    if K % 8 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+    if K % 8 or w.stride(0) % 8 or w.data_ptr() % 16 or \
+            (a is not None and (a.stride(0) % 8 or a.data_ptr() % 16)):
         raise UnsupportedShape(f"gemm_skinny: K={K} and the row pitches must be multiples of 8 elements, "
                                "operands 16-byte aligned")
     if residual is not None and (residual.dtype != torch.float32 or residual.stride(1) != 1
@@ -387,10 +427,25 @@ def gemm_skinny(a, w, bias, out, *, act=None, residual=None) -> None:
         raise KernelError("gemm_skinny: residual must be float32 [M, N]")
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N):
         raise KernelError("gemm_skinny: bias must be bfloat16 [N]")
+    kc = vc = table = tseq = tpos = None
+    page_stride = max_blocks = q_cols = kv_cols = head_dim = page_size = num_pages = 0
+    if kv is not None:
+        hkv, page_size, head_dim, page_stride, num_pages = _cache_args(kv.k_cache, kv.v_cache)
+        kc, vc, table, tseq, tpos = kv.k_cache, kv.v_cache, kv.block_table, kv.token_seq, kv.positions
+        _cuda(kc, vc, table, tseq, tpos)
+        _i32(table, "block_table"); _i32(tseq, "token_seq"); _i32(tpos, "positions")
+        q_cols, kv_cols, max_blocks = kv.q_cols, kv.kv_cols, table.shape[1]
+        if kc.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kv_cols != hkv * head_dim \
+                or q_cols + 2 * kv_cols != N or kv.head_dim != head_dim:
+            raise KernelError("gemm_skinny: the key/value target does not match the product")
     lib = load_library("gemm_skinny")
-    code = lib.sandy_gemm_skinny(_p(a), _p(w), _p(bias), _p(residual), _p(out), ctypes.c_int(M), ctypes.c_int(N),
-                                 ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
-                                 ctypes.c_int(0 if residual is None else residual.stride(0)),
-                                 ctypes.c_int(out.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(out)),
-                                 _stream())
-    _check(code, f"gemm_skinny(M={M},N={N},K={K})")
+    code = lib.sandy_gemm_skinny(
+        _p(a), _p(x), ctypes.c_int(0 if x is None else x.stride(0)), _p(gamma), _p(beta), ctypes.c_float(eps),
+        _p(w), _p(bias), _p(residual), _p(out), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_int(0 if a is None else a.stride(0)), ctypes.c_int(w.stride(0)),
+        ctypes.c_int(0 if residual is None else residual.stride(0)), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(out)), _p(kc), _p(vc), ctypes.c_longlong(page_stride),
+        _p(table), ctypes.c_int(max_blocks), _p(tseq), _p(tpos), ctypes.c_int(q_cols), ctypes.c_int(kv_cols),
+        ctypes.c_int(head_dim), ctypes.c_int(page_size), ctypes.c_int(num_pages), _p(kernel_status(w.device)),
+        _stream())
+    _check(code, f"gemm_skinny(M={M},N={N},K={K},norm={norm is not None},kv={kv is not None})")

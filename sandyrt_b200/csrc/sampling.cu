@@ -105,6 +105,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
     __shared__ int iscratch[32];
     __shared__ float best_val_s[32];
     __shared__ int best_idx_s[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -310,7 +312,6 @@ SANDY_API int sandy_sample(const float* logits, int ld, int n_rows, int vocab,
     if (n_rows == 0) return SANDY_OK;
     if (!logits || !out_token || vocab <= 0) return SANDY_ERR_ARGUMENT;
     if (temperature && !uniform) return SANDY_ERR_ARGUMENT;
-    sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p,
-                                                  uniform, out_token, status);
-    return sandy_launch_status();
+    return sandy_launch(sample_kernel, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, vocab, temperature, top_k,
+                        top_p, uniform, out_token, status);
 }

@@ -22,10 +22,12 @@ from ..csrc import ops
 from ..registry import register_part
 from ..weights.loader import TensorRequest
 from .base import LayerCallCtx, Mixer, PagedKVSpec, StepContext
-from .linear import Linear
+from .linear import KVTarget, Linear
 
 
 class CausalSelfAttention(Mixer):
+    accepts_lazy_norm = True     # `h` may arrive as a LazyNorm; the q/k/v projection runs it
+
     def __init__(self, spec):
         super().__init__(spec)
         self.width = int(self._param("width"))
@@ -61,15 +63,22 @@ class CausalSelfAttention(Mixer):
         T = h.shape[0]
         ws = ctx.workspace
         qkv = ws.get("qkv", T, self.q_cols + 2 * self.kv_cols, ctx.compute_dtype)
-        self.qkv(h, qkv)
+        k_cache, v_cache, group = ctx.caches.kv(call.cache)
+        table = ctx.block_tables[group]
+        rotates = ctx.position is not None and getattr(ctx.position, "rotates", False)
+        # keys/values may go straight from the projection's write-back into the pages, unless
+        # a position encoding still has to turn them first
+        target = None
+        if call.write_cache and not rotates:
+            target = KVTarget(k_cache, v_cache, table, ctx.token_seq, ctx.positions, self.q_cols, self.kv_cols,
+                              self.head_dim)
+        self.qkv(h, qkv, kv=target)
         q = qkv[:, :self.q_cols]
         k = qkv[:, self.q_cols:self.q_cols + self.kv_cols]
         v = qkv[:, self.q_cols + self.kv_cols:]
-        if ctx.position is not None:
+        if rotates:
             ctx.position.rotate(ctx, q, k if call.write_cache else None)
-        k_cache, v_cache, group = ctx.caches.kv(call.cache)
-        table = ctx.block_tables[group]
-        if call.write_cache:
+        if call.write_cache and not (target is not None and target.written):
             ops.kv_append(k, v, k_cache, v_cache, table, ctx.token_seq, ctx.positions)
         o = ws.get("attn_out", T, self.q_cols, ctx.compute_dtype)
         ops.attention(ctx, q, k_cache, v_cache, table, o, n_heads=self.n_heads, scale=self.scale,

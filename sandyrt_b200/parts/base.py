@@ -142,6 +142,7 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     max_positions: Optional[int] = None
+    rotates = False      # True for encodings that act on queries and keys (`rotate`)
 
     def table(self) -> Optional[torch.Tensor]:
         return None

@@ -2,18 +2,59 @@
 
 The weight file may store a matrix as [in, out] (GPT-2's Conv1D layout; the reference
 transposes these offline, scripts/run_gpt2.py:177-189) or as [out, in].  Both are read as
-they are: the 32-bit kernel takes either layout, and for the tensor-core kernel the matrix
-is brought into [out, in] once, when it is bound, which is the K-major operand layout that
-kernel reads.
+they are: the 32-bit kernel takes either layout, and for the tensor-core kernels the matrix
+is brought into [out, in] once, when it is bound, which is the K-major operand layout those
+kernels read.
+
+Kernel choice per call, by dtype and row count: float32 -> the FFMA kernel; bfloat16 with up
+to 64 rows (a decode step) -> the weight-streaming kernel, which can also run the norm before
+the product and write key/value columns into the cache; bfloat16 with more rows -> tcgen05.
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict, Optional
 
 import torch
 
 from ..csrc import ops
 from ..weights.loader import TensorRequest
+
+
+class LazyNorm:
+    """A normed view of the residual stream that has not been computed yet.  A consumer either
+    asks for the tensor (`tensor()`, computed once and shared) or, if its kernel can run the
+    norm itself, reads `x` and `norm` and never materialises it."""
+
+    def __init__(self, ctx, norm, x: torch.Tensor, out_dtype: torch.dtype):
+        self.ctx, self.norm, self.x, self.out_dtype = ctx, norm, x, out_dtype
+        self._tensor: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            h = self.ctx.workspace.get("normed", self.x.shape[0], self.x.shape[1], self.out_dtype)
+            self.norm.forward(self.ctx, self.x, h)
+            self._tensor = h
+        return self._tensor
+
+
+@dataclasses.dataclass
+class KVTarget:
+    """Where the key/value columns of a fused q/k/v product belong: the layer's cache views and
+    the step's index arrays.  `written` is set by the product if its kernel did the write."""
+    k_cache: torch.Tensor
+    v_cache: torch.Tensor
+    block_table: torch.Tensor
+    token_seq: torch.Tensor
+    positions: torch.Tensor
+    q_cols: int
+    kv_cols: int
+    head_dim: int
+    written: bool = False
 
 
 class Linear:
@@ -57,13 +98,27 @@ class Linear:
             n += self.bias.numel() * self.bias.element_size()
         return n
 
-    def __call__(self, a: torch.Tensor, out: torch.Tensor, *, act: Optional[str] = None,
-                 residual: Optional[torch.Tensor] = None) -> None:
-        """out = act(a @ W + b) + residual.  `out` may be `residual` itself."""
+    def __call__(self, a, out: torch.Tensor, *, act: Optional[str] = None,
+                 residual: Optional[torch.Tensor] = None, kv: Optional[KVTarget] = None) -> None:
+        """out = act(a @ W + b) + residual.  `out` may be `residual` itself.  `a` is a tensor or a
+        LazyNorm.  If `kv` is given and the kernel used can write keys/values into the cache, it
+        does and sets `kv.written`; otherwise the caller appends them itself."""
+        rows = a.shape[0]
+        if self.use_tensor_cores and rows <= ops.SKINNY_MAX_ROWS:
+            norm = None
+            if isinstance(a, LazyNorm):
+                if ops.skinny_norm_fusable(a, self.in_features):
+                    norm = a
+                    a = None
+                else:
+                    a = a.tensor()
+            ops.gemm_skinny(a, self.weight, self.bias, out, act=act, residual=residual, norm=norm, kv=kv)
+            if kv is not None:
+                kv.written = True
+            return
+        if isinstance(a, LazyNorm):
+            a = a.tensor()
         if self.use_tensor_cores:
-            if a.shape[0] <= ops.SKINNY_MAX_ROWS:
-                ops.gemm_skinny(a, self.weight, self.bias, out, act=act, residual=residual)
-            else:
-                ops.gemm_tc(a, self.weight, self.bias, out, act=act, residual=residual)
+            ops.gemm_tc(a, self.weight, self.bias, out, act=act, residual=residual)
         else:
             ops.gemm_simt(a, self.weight, self.bias, out, w_out_in=self.w_out_in, act=act, residual=residual)

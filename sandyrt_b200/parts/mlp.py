@@ -20,6 +20,8 @@ from .linear import Linear
 
 
 class DenseMLP(FeedForward):
+    accepts_lazy_norm = True     # `h` may arrive as a LazyNorm; the up-projection runs it
+
     def __init__(self, spec):
         super().__init__(spec)
         self.width = int(self._param("width"))

@@ -17,6 +17,8 @@ from .base import Norm, StepContext
 
 
 class LayerNorm(Norm):
+    fusable_kind = "layernorm"     # kernels that can run a norm inside themselves recognise it by this
+
     def __init__(self, spec):
         super().__init__(spec)
         self.width = int(self._param("width"))

@@ -266,6 +266,13 @@ def test_decode_attention_split_kv(dtype, H, Hkv, D, page_size, window, splits):
     ops.check_kernel_status(DEV)
     want = _attention_want(case, H, Hkv, D, scale, window)
     assert (out.double().cpu() - want).abs().max().item() < ATT_TOL[dtype]
+    # the same splits as one cluster, merged through distributed shared memory: same numbers
+    if splits > 1:
+        out2 = torch.full_like(case["q"], float("nan"))
+        ops.decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"], out2,
+                             n_heads=H, scale=scale, window=window, num_splits=splits, cluster=True)
+        ops.check_kernel_status(DEV)
+        assert torch.equal(out2, out)
 
 
 @pytest.mark.parametrize("kernel", ["general", "decode"])
@@ -359,3 +366,74 @@ def test_gemm_skinny(M, N, K):
     x = res.clone()
     ops.gemm_skinny(a, w_nk, None, x, residual=x)
     assert (x.double() - (res.double() + a.double() @ w_nk.double().t())).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("K,N,eps", [(64, 192, 1e-5), (768, 2304, 1e-5), (96, 320, 1e-6), (240, 777, 3e-5), (1600, 136, 1e-5), (2048, 64, 1e-5)])
+def test_gemm_skinny_with_the_norm_inside(M, K, N, eps):
+    """LayerNorm run inside the product equals the stand-alone norm kernel followed by the product."""
+    from sandyrt_b200.csrc import ops
+    from sandyrt_b200.parts.linear import LazyNorm
+
+    class N_:                                    # the fields of a LayerNorm part the kernel reads
+        fusable_kind = "layernorm"
+    norm = N_()
+    norm.gamma, norm.beta, norm.eps = _rand((K,), torch.bfloat16, 4) + 1.0, _rand((K,), torch.bfloat16, 5), eps
+    x = _rand((M, K), torch.float32, 1, scale=2.0) + 0.3
+    w = _rand((N, K), torch.bfloat16, 2, scale=0.1)
+    bias = _rand((N,), torch.bfloat16, 3)
+    lazy = LazyNorm(None, norm, x, torch.bfloat16)
+    assert ops.skinny_norm_fusable(lazy, K)
+    got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(None, w, bias, got, act="gelu_new", norm=lazy)
+    h = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    ops.layernorm(x, norm.gamma, norm.beta, eps, h)
+    want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(h, w, bias, want, act="gelu_new")
+    # the two norms add in another order: an element of h may round the other way now and then
+    assert (got.float() - want.float()).abs().max().item() < 2e-2 * (1 + want.float().abs().max().item())
+    xd = x.double()
+    hd = ((xd - xd.mean(-1, keepdim=True)) / torch.sqrt(xd.var(-1, unbiased=False, keepdim=True) + eps)
+          * norm.gamma.double() + norm.beta.double())
+    ref = _gemm_want(hd, w.t(), bias, "gelu_new", None)
+    assert (got.double() - ref).abs().max().item() < 2e-2 * (1 + ref.abs().max().item())
+
+
+def test_gemm_skinny_writes_keys_and_values_into_the_pages():
+    """The fused q/k/v product puts its key and value columns where kv_append would."""
+    from sandyrt_b200.csrc import ops
+    from sandyrt_b200.parts.linear import KVTarget
+
+    H, Hkv, D, ps = 6, 2, 32, 8
+    q_cols, kv_cols = H * D, Hkv * D
+    K = 96
+    seqs = [(13, 1), (0, 1), (7, 1), (40, 1), (8, 3)]
+    T = sum(n for _, n in seqs)
+    num_pages = 32
+    g = torch.Generator().manual_seed(0)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((len(seqs), 8), -1, dtype=torch.int32)
+    tok_seq, tok_pos = [], []
+    for s, (before, n) in enumerate(seqs):
+        for b in range(-(-(before + n) // ps)):
+            table[s, b] = perm.pop()
+        tok_seq += [s] * n
+        tok_pos += list(range(before, before + n))
+    table = table.to(DEV)
+    tok_seq = torch.tensor(tok_seq, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(tok_pos, dtype=torch.int32, device=DEV)
+    a = _rand((T, K), torch.bfloat16, 1)
+    w = _rand((q_cols + 2 * kv_cols, K), torch.bfloat16, 2, scale=0.2)
+    bias = _rand((q_cols + 2 * kv_cols,), torch.bfloat16, 3)
+    arena_a = torch.zeros(num_pages, 2, Hkv, ps, D, dtype=torch.bfloat16, device=DEV)
+    arena_b = torch.zeros_like(arena_a)
+    out_a = torch.empty(T, q_cols + 2 * kv_cols, dtype=torch.bfloat16, device=DEV)
+    out_b = torch.empty_like(out_a)
+    target = KVTarget(arena_a[:, 0], arena_a[:, 1], table, tok_seq, tok_pos, q_cols, kv_cols, D)
+    ops.gemm_skinny(a, w, bias, out_a, kv=target)
+    ops.gemm_skinny(a, w, bias, out_b)
+    ops.kv_append(out_b[:, q_cols:q_cols + kv_cols], out_b[:, q_cols + kv_cols:], arena_b[:, 0], arena_b[:, 1],
+                  table, tok_seq, tok_pos)
+    ops.check_kernel_status(DEV)
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(arena_a, arena_b) and float(arena_a.abs().sum()) > 0
