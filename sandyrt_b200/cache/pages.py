@@ -126,6 +126,7 @@ class _Request:
     slot: int
     length: int                       # tokens whose keys/values are in the cache
     blocks: List[List[int]]           # per group: page id per block index, FREED where given back
+    version: int = 0                  # changes whenever a block list changes (never reused)
 
 
 class BlockAllocator:
@@ -147,6 +148,7 @@ class BlockAllocator:
         self.max_requests = max_requests
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._requests: Dict[Hashable, _Request] = {}
+        self._stamp = 0
 
     # ---- queries ---------------------------------------------------------------------
     def __contains__(self, rid) -> bool:
@@ -166,6 +168,11 @@ class BlockAllocator:
 
     def length(self, rid) -> int:
         return self._get(rid).length
+
+    def block_version(self, rid) -> int:
+        """A number that changes whenever any of the request's block lists changes; a request
+        that is released and admitted again under the same id gets a new one."""
+        return self._get(rid).version
 
     def block_list(self, rid, group: int) -> List[int]:
         return self._get(rid).blocks[group]
@@ -204,7 +211,8 @@ class BlockAllocator:
         if not self._free_slots:
             raise NoFreeSlot(f"all {self.max_requests} state slots are in use")
         slot = self._free_slots.pop()
-        self._requests[rid] = _Request(slot, 0, [[] for _ in self.pools])
+        self._stamp += 1
+        self._requests[rid] = _Request(slot, 0, [[] for _ in self.pools], self._stamp)
         return slot
 
     def reserve(self, rid, new_len: int) -> None:
@@ -217,7 +225,10 @@ class BlockAllocator:
                 raise OutOfPages(f"group {g}: request {rid!r} needs {n} more pages for {new_len} tokens, "
                                  f"{pool.free_pages} of {pool.num_pages} free")
         for bl, n, pool in zip(r.blocks, need, self.pools):
-            bl.extend(pool.allocate(n))
+            if n:
+                bl.extend(pool.allocate(n))
+                self._stamp += 1
+                r.version = self._stamp
 
     def commit(self, rid, new_len: int) -> None:
         r = self._get(rid)
@@ -234,6 +245,8 @@ class BlockAllocator:
                 self.pools[g].release(gone)
                 for i in range(first):
                     bl[i] = FREED
+                self._stamp += 1
+                r.version = self._stamp
 
     def release(self, rid) -> None:
         r = self._get(rid)

@@ -37,9 +37,8 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int COLS = 8;          // output columns per block
 constexpr int KCHUNK = 32;       // k covered by one 16-byte load of every lane
-constexpr int UNROLL = 4;
 constexpr int XPAD = 32;         // elements of padding per shared-memory row (64 bytes: conflict-free 16-byte reads)
-constexpr int MAX_ROW_VEC = 16;  // float4 per lane a fused-norm row may take: K <= 2048
+constexpr int MAX_ROW_VEC = 16;  // most float4 per lane a fused-norm row may take: K <= 2048
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -80,9 +79,12 @@ struct NormArgs {
     float eps;
 };
 
-// MT: number of 16-row token tiles (M <= 16 * MT)
-template <int MT, typename TC, bool FUSE_LN>
-__global__ void __launch_bounds__(WARPS * 32)
+// MT: number of 16-row token tiles (M <= 16 * MT).  UNROLL: 16-byte weight pieces a lane keeps in
+// flight per round (chosen so that a warp's whole K slice is one or two rounds).  RV: float4 per
+// lane that hold a row during the fused norm (K <= 128 * RV); sized to K so that registers,
+// and with them the number of resident blocks, are not wasted on short rows.
+template <int MT, typename TC, bool FUSE_LN, int UNROLL, int RV>
+__global__ void __launch_bounds__(WARPS * 32, (UNROLL == 4 && RV <= 8 && MT == 1) ? 3 : 1)
 gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __restrict__ w,
                    const bf16* __restrict__ bias, const float* residual, TC* out, int M, int N, int K, int lda,
                    int ldw, int ldr, int ldc, int act, KVWrite kv) {
@@ -125,6 +127,18 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
     pdl_launch_dependents();
     pdl_wait();
 
+    // The page this thread's key/value element goes to (two dependent loads): asked for now,
+    // needed only in the write-back.
+    int kv_page = -1, kv_pos = 0;
+    if (kv.k_cache && MT == 1 && threadIdx.x < 16 * COLS) {
+        const int m = threadIdx.x / COLS;
+        if (m < M && n0 + (int)(threadIdx.x % COLS) >= kv.q_cols) {
+            kv_pos = kv.positions[m];
+            const int b = kv_pos / kv.page_size;
+            kv_page = (kv_pos >= 0 && b < kv.max_blocks) ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
+        }
+    }
+
     if (FUSE_LN) {
         // warp per row; the row lives in registers between the passes
         for (int r = warp; r < MT * 16; r += WARPS) {
@@ -134,10 +148,10 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
                 continue;
             }
             const float* xr = norm.x + (size_t)r * norm.ldx;
-            float4 v[MAX_ROW_VEC];
+            float4 v[RV];
             float s = 0.0f;
 #pragma unroll
-            for (int i = 0; i < MAX_ROW_VEC; i++) {
+            for (int i = 0; i < RV; i++) {
                 const int k = (i * 32 + lane) * 4;
                 v[i] = k < K ? *reinterpret_cast<const float4*>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
                 s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
@@ -145,7 +159,7 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
             const float mean = warp_sum(s) / (float)K;
             float q = 0.0f;
 #pragma unroll
-            for (int i = 0; i < MAX_ROW_VEC; i++) {
+            for (int i = 0; i < RV; i++) {
                 const int k = (i * 32 + lane) * 4;
                 if (k < K) {
                     const float cx = v[i].x - mean, cy = v[i].y - mean, cz = v[i].z - mean, cw = v[i].w - mean;
@@ -154,7 +168,7 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
             }
             const float inv = 1.0f / sqrtf(warp_sum(q) / (float)K + norm.eps);
 #pragma unroll
-            for (int i = 0; i < MAX_ROW_VEC; i++) {
+            for (int i = 0; i < RV; i++) {
                 const int k = (i * 32 + lane) * 4;
                 if (k < K) {
                     const uint2 gm = *reinterpret_cast<const uint2*>(norm.gamma + k);
@@ -235,10 +249,12 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
             const bool is_v = c >= kv.kv_cols;
             const int c2 = is_v ? c - kv.kv_cols : c;
             const int head = c2 / kv.head_dim, d = c2 % kv.head_dim;
-            const int pos = kv.positions[m];
-            const int b = pos / kv.page_size;
-            const int page = (pos >= 0 && b < kv.max_blocks)
-                                 ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
+            int pos = kv_pos, page = kv_page;
+            if (MT != 1) {
+                pos = kv.positions[m];
+                const int b = pos / kv.page_size;
+                page = (pos >= 0 && b < kv.max_blocks) ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
+            }
             if (page < 0 || page >= kv.num_pages) {
                 if (kv.status) atomicOr(kv.status, 8);
             } else {
@@ -250,14 +266,14 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
     }
 }
 
-template <int MT, bool FUSE_LN>
-int launch(const void* a, const NormArgs& norm, const void* w, const void* bias, const float* residual, void* out,
-           int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype, const KVWrite& kv,
-           cudaStream_t stream) {
+template <int MT, bool FUSE_LN, int UNROLL, int RV>
+int launch2(const void* a, const NormArgs& norm, const void* w, const void* bias, const float* residual, void* out,
+            int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype, const KVWrite& kv,
+            cudaStream_t stream) {
     const unsigned blocks = (unsigned)((N + COLS - 1) / COLS);
     const size_t smem = FUSE_LN ? (size_t)MT * 16 * (K + XPAD) * sizeof(bf16) : 0;
     if (out_dtype == SANDY_F32) {
-        auto kern = gemm_skinny_kernel<MT, float, FUSE_LN>;
+        auto kern = gemm_skinny_kernel<MT, float, FUSE_LN, UNROLL, RV>;
         if (smem > 40 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
@@ -265,7 +281,7 @@ int launch(const void* a, const NormArgs& norm, const void* w, const void* bias,
         return sandy_launch(kern, dim3(blocks), dim3(WARPS * 32), smem, stream, (const bf16*)a, norm, (const bf16*)w,
                             (const bf16*)bias, residual, (float*)out, M, N, K, lda, ldw, ldr, ldc, act, kv);
     } else {
-        auto kern = gemm_skinny_kernel<MT, bf16, FUSE_LN>;
+        auto kern = gemm_skinny_kernel<MT, bf16, FUSE_LN, UNROLL, RV>;
         if (smem > 40 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
@@ -273,6 +289,30 @@ int launch(const void* a, const NormArgs& norm, const void* w, const void* bias,
         return sandy_launch(kern, dim3(blocks), dim3(WARPS * 32), smem, stream, (const bf16*)a, norm, (const bf16*)w,
                             (const bf16*)bias, residual, (bf16*)out, M, N, K, lda, ldw, ldr, ldc, act, kv);
     }
+}
+
+template <int MT, bool FUSE_LN, int RV>
+int launch1(const void* a, const NormArgs& norm, const void* w, const void* bias, const float* residual, void* out,
+            int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype, const KVWrite& kv,
+            cudaStream_t stream) {
+    // 16-byte pieces of one warp's K slice
+    const int per_warp = ((K + KCHUNK - 1) / KCHUNK + WARPS - 1) / WARPS;
+    if (per_warp <= 4)
+        return launch2<MT, FUSE_LN, 4, RV>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    if (per_warp <= 8 || MT > 1)
+        return launch2<MT, FUSE_LN, 8, RV>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    return launch2<MT, FUSE_LN, 16, RV>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+}
+
+template <int MT, bool FUSE_LN>
+int launch(const void* a, const NormArgs& norm, const void* w, const void* bias, const float* residual, void* out,
+           int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype, const KVWrite& kv,
+           cudaStream_t stream) {
+    if (!FUSE_LN || K <= 512)
+        return launch1<MT, FUSE_LN, 4>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    if (K <= 1024)
+        return launch1<MT, FUSE_LN, 8>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    return launch1<MT, FUSE_LN, 16>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
 }
 
 }  // namespace

@@ -299,8 +299,12 @@ def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale
                     n_heads=n_heads, scale=scale, window=window)
 
 
-def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, uniform=None, status=None) -> None:
-    """Choose one token per row of float32 `logits`; per-row option tensors may be None."""
+def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, uniform=None, status=None,
+           feedback=None) -> None:
+    """Choose one token per row of float32 `logits`; per-row option tensors may be None.
+    feedback: (token_ids, logit_rows, positions, burst_tokens, row_step) int32 device tensors: the
+    drawn token also replaces the row's input token, its position moves on, and the token is
+    recorded in burst_tokens[row_step[r], r]; `uniform` then holds [steps, rows] numbers."""
     _cuda(logits, out_tokens, temperature, top_k, top_p, uniform, status)
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 with unit inner stride")
@@ -308,14 +312,25 @@ def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, unif
     _i32(out_tokens, "out_tokens")
     for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
                         ("top_p", top_p, torch.float32), ("uniform", uniform, torch.float32)):
+        if name == "uniform" and feedback is not None:
+            continue
         if t is not None and (t.dtype != dt or t.numel() != n or not t.is_contiguous()):
             raise KernelError(f"sample: {name} must be a contiguous {dt} tensor of one value per row")
     if temperature is not None and uniform is None:
         raise KernelError("sample: temperature sampling needs a uniform number per row")
+    fb = [None] * 5
+    if feedback is not None:
+        fb = list(feedback)
+        _cuda(*fb)
+        for t in fb:
+            _i32(t, "feedback array")
+        if uniform is None or uniform.dtype != torch.float32 or not uniform.is_contiguous() \
+                or uniform.numel() % n or fb[3].numel() < uniform.numel():
+            raise KernelError("sample: with feedback, uniform must be float32 [steps, rows] and burst_tokens as large")
     lib = load_library("sampling")
     code = lib.sandy_sample(_p(logits), ctypes.c_int(logits.stride(0)), ctypes.c_int(n), ctypes.c_int(vocab),
                             _p(temperature), _p(top_k), _p(top_p), _p(uniform), _p(out_tokens), _p(status),
-                            _stream())
+                            _p(fb[0]), _p(fb[1]), _p(fb[2]), _p(fb[3]), _p(fb[4]), _stream())
     _check(code, "sample")
 
 

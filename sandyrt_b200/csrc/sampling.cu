@@ -94,13 +94,39 @@ __device__ __forceinline__ int block_exclusive_scan_int(int v, int* scratch, int
     return warp_prefix + (inc - v);
 }
 
+// Feeding the drawn token straight back into the next decode step, on the device.  When
+// `token_ids` is set, the row's token is also written over the step's input token of that row
+// (token_ids[logit_rows[r]]), the row's position moves on by one, and the token is recorded
+// in out_tokens[step * n_rows + r], where `step` is the row's own counter row_step[r] (it also
+// selects the row's uniform number, uniform[step * n_rows + r]).  A whole run of decode steps
+// can then be replayed back to back with no trip to the host in between.
+struct Advance {
+    int* token_ids;
+    const int* logit_rows;
+    int* positions;
+    int* out_tokens;
+    int* row_step;
+    int n_rows;
+};
+
+__device__ __forceinline__ void emit_token(int r, int tok, int* __restrict__ out_token, const Advance& adv, int step) {
+    out_token[r] = tok;
+    if (adv.token_ids) {
+        const int t = adv.logit_rows[r];
+        adv.token_ids[t] = tok;
+        adv.positions[t] += 1;
+        adv.out_tokens[(size_t)step * adv.n_rows + r] = tok;
+        adv.row_step[r] = step + 1;
+    }
+}
+
 // One block per row.  Each thread owns the contiguous id range [begin, end) so that
 // "in id order" is "in thread order, then in the thread's own order".
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ uniform,
-              int* __restrict__ out_token, int* __restrict__ status) {
+              int* __restrict__ out_token, int* __restrict__ status, Advance adv) {
     __shared__ float fscratch[32];
     __shared__ int iscratch[32];
     __shared__ float best_val_s[32];
@@ -110,6 +136,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int step = adv.token_ids ? adv.row_step[r] : 0;
     const int per = (vocab + THREADS - 1) / THREADS;
     const int begin = min(vocab, tid * per), end = min(vocab, begin + per);
 
@@ -139,12 +166,12 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     if (has_nan) {
-        if (tid == 0) { out_token[r] = -1; if (status) atomicOr(status, 1); }
+        if (tid == 0) { emit_token(r, -1, out_token, adv, step); if (status) atomicOr(status, 1); }
         return;
     }
     const float T = temperature ? temperature[r] : 0.0f;
     if (T == 0.0f || !isfinite(bv)) {
-        if (tid == 0) out_token[r] = bi;
+        if (tid == 0) emit_token(r, bi, out_token, adv, step);
         return;
     }
     const float best = bv;
@@ -262,7 +289,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
     const float prefix = block_exclusive_scan(mine, fscratch, &kept_total);
 
     // ---- inverse CDF in id order -----------------------------------------------------------
-    const float target = uniform[r] * kept_total;
+    const float target = uniform[(size_t)step * (adv.token_ids ? adv.n_rows : 0) + r] * kept_total;
     // The thread whose [prefix, prefix+mine) holds the target walks its range.  The last
     // thread with any weight also takes targets that rounding pushed past the end.
     __shared__ int chosen;
@@ -298,7 +325,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
         if (tid == 0) chosen = last_kept >= 0 ? last_kept : bi;
         __syncthreads();
     }
-    if (tid == 0) out_token[r] = chosen;
+    if (tid == 0) emit_token(r, chosen, out_token, adv, step);
 }
 
 }  // namespace
@@ -306,12 +333,20 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
 // logits: float [n_rows, vocab] with row stride ld.  temperature, top_k, top_p, uniform:
 // per-row arrays on the device (temperature null = greedy for all rows; top_k null = no
 // cut; top_p null = 1).  out_token: int32[n_rows].
+// Feedback (all null to switch it off): token_ids / positions are the step's input arrays,
+// logit_rows[r] the input row that row r's token replaces, out_tokens an int32 array of
+// [steps][n_rows], row_step int32[n_rows] counters (start them at 0); `uniform` then holds
+// [steps][n_rows] numbers.
 SANDY_API int sandy_sample(const float* logits, int ld, int n_rows, int vocab,
                            const float* temperature, const int* top_k, const float* top_p,
-                           const float* uniform, int* out_token, int* status, cudaStream_t stream) {
+                           const float* uniform, int* out_token, int* status, int* token_ids,
+                           const int* logit_rows, int* positions, int* out_tokens, int* row_step,
+                           cudaStream_t stream) {
     if (n_rows == 0) return SANDY_OK;
     if (!logits || !out_token || vocab <= 0) return SANDY_ERR_ARGUMENT;
     if (temperature && !uniform) return SANDY_ERR_ARGUMENT;
+    if (token_ids && (!logit_rows || !positions || !out_tokens || !row_step)) return SANDY_ERR_ARGUMENT;
+    Advance adv{token_ids, logit_rows, positions, out_tokens, row_step, n_rows};
     return sandy_launch(sample_kernel, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, vocab, temperature, top_k,
-                        top_p, uniform, out_token, status);
+                        top_p, uniform, out_token, status, adv);
 }

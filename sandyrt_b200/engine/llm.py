@@ -19,15 +19,16 @@ from __future__ import annotations
 import dataclasses
 import sys
 import time
-from typing import Callable, Dict, Hashable, List, Optional, Sequence, Union
+from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple, Union
 
+import numpy as np
 import torch
 
 from ..models.model import Model, load_model
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import fresh_seed, uniform_for
-from .scheduler import Request, RequestRefused, RequestState, Scheduler, StepPlan
-from .step import Engine, SampleRow, StepEntry
+from .scheduler import Portion, Request, RequestRefused, RequestState, Scheduler, StepPlan
+from .step import MAX_BURST, Engine, SampleRow, StepEntry
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -55,11 +56,14 @@ class LLM:
                  cache_tokens: Optional[int] = None, page_size: int = 16, max_live: int = 64,
                  max_step_tokens: int = 2048, prefill_chunk_tokens: int = 2048,
                  eos_token_ids: Optional[Sequence[int]] = None, max_context_tokens: int = 0,
-                 use_cuda_graphs: bool = True):
+                 use_cuda_graphs: bool = True, max_burst: int = 8):
         """cache_tokens: how many tokens the cache pool holds (default: room for `max_live`
         requests of full length, capped at 1M tokens).  eos_token_ids: stop tokens added to
         every request (default: the config's eos_token_id is NOT added; pass it to stop there).
-        max_context_tokens: if > 0, a lower limit on a request's length than the model's."""
+        max_context_tokens: if > 0, a lower limit on a request's length than the model's.
+        max_burst: most decode steps run on the device between two looks of the host (1 = the
+        host sees every token as it is drawn; more = fewer round trips, tokens arrive in groups,
+        and up to max_burst - 1 steps of a request that has just hit a stop token are wasted)."""
         if not torch.cuda.is_available():
             raise RuntimeError("sandyrt_b200 needs a CUDA device; there is no CPU path")
         if isinstance(model, Model):
@@ -78,6 +82,8 @@ class LLM:
                                    prefill_chunk=prefill_chunk_tokens, max_live=max_live,
                                    max_positions=limit)
         self.eos_token_ids = frozenset(int(t) for t in (eos_token_ids or ()))
+        self.max_burst = max(1, min(int(max_burst), MAX_BURST)) if self.engine.use_cuda_graphs else 1
+        self.decode_steps_run = 0
         self._requests: Dict[Hashable, Request] = {}
         self._seeds: Dict[Hashable, int] = {}
         self._next_id = 0
@@ -108,11 +114,72 @@ class LLM:
     def has_work(self) -> bool:
         return self.scheduler.has_work()
 
-    def step(self) -> List[Request]:
-        """Plan and run one step.  Returns the requests that received a token in it."""
+    def _burst_length(self, plan: StepPlan) -> int:
+        """How many decode steps may run on the device before the host looks again: more than
+        one only when every request of the step is decoding and nobody waits to be admitted,
+        and never past a request's token limit, the model's positions or the free pages."""
+        if self.max_burst <= 1 or self.scheduler.waiting or not plan.portions:
+            return 1
+        n = self.max_burst
+        for p in plan.portions:
+            r = p.request
+            if p.count != 1 or not p.samples or not r.output:
+                return 1
+            n = min(n, r.max_tokens - len(r.output))
+            if self.max_positions is not None:
+                n = min(n, self.max_positions - r.computed)
+        alloc = self.engine.cache.alloc
+        while n > 1:
+            need = [0] * len(alloc.pools)
+            for p in plan.portions:
+                for g, k in enumerate(alloc.pages_needed(p.request.rid, p.request.computed + n)):
+                    need[g] += k
+            if all(k <= alloc.free_pages(g) for g, k in enumerate(need)):
+                break
+            n //= 2
+        return max(n, 1)
+
+    def _step_burst(self, plan: StepPlan, n: int) -> List[Tuple[Request, int]]:
+        """n decode steps in one go (Engine.decode_burst), then the scheduler's bookkeeping for
+        each of them in order.  A request that finishes part of the way keeps only the tokens up
+        to its finish; what the device computed for it after that is dropped."""
+        reqs = [p.request for p in plan.portions]
+        entries = [StepEntry(r.rid, [r.tokens[-1]], [0]) for r in reqs]
+        rows, uniforms = [], np.zeros((n, len(reqs)), dtype=np.float32)
+        for i, r in enumerate(reqs):
+            sp = r.sampling
+            rows.append(SampleRow(0.0 if sp.greedy else sp.temperature, sp.top_k, sp.top_p, 0.0))
+            if not sp.greedy:
+                for j in range(n):
+                    uniforms[j, i] = uniform_for(self._seeds[r.rid], len(r.output) + j)
+        tokens = self.engine.decode_burst(entries, rows, uniforms)
+        if (tokens < 0).any():
+            self.engine.check_status()
+            raise ValueError("sampling logits must not contain NaN")         # Sampler.cpp:64-67
+        self.decode_steps_run += n
+        now = time.perf_counter()
+        got: List[Tuple[Request, int]] = []
+        alive = list(range(len(reqs)))
+        for j in range(n):
+            sub = StepPlan([Portion(reqs[i], reqs[i].computed, 1, True) for i in alive], [])
+            sampled = {reqs[i].rid: int(tokens[j, i]) for i in alive}
+            got += [(reqs[i], int(tokens[j, i])) for i in alive]
+            for r in self.scheduler.complete(sub, sampled):
+                r.t_finished = now
+            alive = [i for i in alive if reqs[i].state is RequestState.RUNNING]
+            if not alive:
+                break
+        return got
+
+    def step(self) -> List[Tuple[Request, int]]:
+        """Plan and run one step (or, when every request is decoding, a burst of steps on the
+        device).  Returns (request, token) for every token drawn, in order."""
         plan = self.scheduler.plan()
         if not plan.portions:
             return []
+        n_burst = self._burst_length(plan)
+        if n_burst > 1:
+            return self._step_burst(plan, n_burst)
         now = time.perf_counter()
         entries, sampled_reqs = [], []
         for p in plan.portions:
@@ -148,7 +215,8 @@ class LLM:
                 r.t_first_token = now
         for r in self.scheduler.complete(plan, sampled):
             r.t_finished = now
-        return sampled_reqs
+        self.decode_steps_run += 1
+        return [(r, sampled[r.rid]) for r in sampled_reqs]
 
     def result(self, rid: Hashable) -> GenerateResult:
         r = self._requests[rid]
@@ -184,13 +252,23 @@ class LLM:
                                seed=None if seed is None else seed + i)
             rids.append(self.add_request(p, max_tokens=max_tokens, sampling=s, stop_token_ids=stop_token_ids))
         index = {rid: i for i, rid in enumerate(rids)}
+        cancelled = set()
+        delivered = {rid: 0 for rid in rids}
         while any(self._requests[r].state is not RequestState.FINISHED for r in rids):
             got = self.step()
             if on_token:
-                for r in got:
-                    if r.rid in index and on_token(index[r.rid], r.output[-1]) is False \
-                            and r.state is not RequestState.FINISHED:
-                        self.abort(r.rid)
+                for r, token in got:
+                    if r.rid not in index or r.rid in cancelled:
+                        continue
+                    delivered[r.rid] += 1
+                    if on_token(index[r.rid], token) is False:
+                        # the request ends with the token just delivered; what a burst had
+                        # already drawn beyond it is dropped
+                        cancelled.add(r.rid)
+                        if r.state is not RequestState.FINISHED:
+                            self.abort(r.rid)
+                        del r.output[delivered[r.rid]:]
+                        r.finish_reason = "cancelled"
         results = [self.result(r) for r in rids]
         for r in rids:
             self.forget(r)

@@ -19,6 +19,11 @@ wanted rows, sampling options) are packed on the host into one pinned buffer and
 device with one copy.  Steps in which every request brings a single token (decoding) are
 captured as CUDA graphs, one per (requests, wanted rows, block-table width), and replayed:
 the arrays live at fixed device addresses, so a replay only needs the copy before it.
+
+`Engine.decode_burst` runs several decode steps of the same requests with no trip to the host
+in between: the sampler writes each drawn token over the step's input token and moves the
+position on, so the same recorded graph is simply replayed n times; pages for all n steps are
+reserved beforehand and the drawn tokens of all steps come back in one copy.
 """
 from __future__ import annotations
 
@@ -33,6 +38,8 @@ from ..cache.pages import FREED, OutOfPages
 from ..csrc import ops
 from ..models.model import Model
 from ..parts.base import StepContext, Workspace
+
+MAX_BURST = 32      # most decode steps one decode_burst may run
 
 
 @dataclasses.dataclass
@@ -91,6 +98,14 @@ class _Staging:
         self.events[i].record()
 
 
+@dataclasses.dataclass
+class _Prepared:
+    ctx: StepContext
+    sample: Optional[torch.Tensor]          # [temperature R | top_k R | top_p R | uniform R] (one step)
+    key: Optional[Tuple]                    # graph key, None for steps that are not recorded
+    burst: Optional[Tuple[torch.Tensor, torch.Tensor]] = None    # (uniform [n, R], row_step [R]) of a burst
+
+
 class Engine:
     """A bound model, its cache and the step function over them."""
 
@@ -108,14 +123,17 @@ class Engine:
                                   max_requests=max_requests, device=self.device, dtype=self.dtype)
         self.workspace = Workspace(self.device)
         blocks_cap = -(-(model.max_positions or max_tokens) // page_size) + 8
-        cap = 4 * max_step_tokens + 3 * max_requests + 1 + 4 * max_requests \
+        cap = 4 * max_step_tokens + 3 * max_requests + 1 + (5 + MAX_BURST) * max_requests \
             + len(self.cache.layout.groups) * max_requests * blocks_cap
         self._staging = _Staging(self.device, 1 << (cap - 1).bit_length())
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._sampled = torch.zeros(max(max_requests, 1), dtype=torch.int32, device=self.device)
+        self._burst_tokens = torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, device=self.device)
+        self._burst_host = torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, pin_memory=True)
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
-        self._graphs: Dict[Tuple, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graphs: Dict[Tuple, Tuple] = {}
         self._seen: Dict[Tuple, int] = {}
+        self._table_rows: Dict[Tuple[Hashable, int], Tuple[int, np.ndarray]] = {}
         self.steps_run = 0
         self.graph_replays = 0
         self.stale_graphs = 0
@@ -128,16 +146,35 @@ class Engine:
 
     def release(self, rid: Hashable) -> None:
         self.cache.release(rid)
+        for g in self.cache.layout.groups:
+            self._table_rows.pop((rid, g.index), None)
 
     def length(self, rid: Hashable) -> int:
         return self.cache.alloc.length(rid)
 
-    # ---- the step --------------------------------------------------------------------
-    def _prepare(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]]):
-        """Check the entries, reserve pages, pack the step's arrays and copy them to the device."""
+    # ---- packing a step ----------------------------------------------------------------
+    def _table_row(self, rid: Hashable, group: int) -> np.ndarray:
+        """A request's block list as an int32 array, rebuilt only when the list has changed
+        (a page was added, or a window gave pages back)."""
+        stamp = self.cache.alloc.block_version(rid)
+        hit = self._table_rows.get((rid, group))
+        if hit is None or hit[0] != stamp:
+            hit = (stamp, np.asarray(self.cache.alloc.block_list(rid, group), dtype=np.int32))
+            self._table_rows[(rid, group)] = hit
+            if len(self._table_rows) > 4 * self.cache.max_requests * max(1, len(self.cache.layout.groups)):
+                live = self.cache.alloc
+                self._table_rows = {k: v for k, v in self._table_rows.items() if k[0] in live}
+        return hit[1]
+
+    def _prepare(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]],
+                 burst_uniform: Optional[np.ndarray] = None) -> _Prepared:
+        """Check the entries, reserve pages, pack the step's arrays and copy them to the device.
+        burst_uniform: float32 [n_steps, R] for a burst of n_steps decode steps."""
         alloc = self.cache.alloc
         if not entries:
             raise StepError("a step needs at least one token")
+        n_burst = 0 if burst_uniform is None else burst_uniform.shape[0]
+        extra = max(n_burst - 1, 0)              # positions a burst adds beyond this step's
         seen = set()
         q_lens, kv_before, slots = [], [], []
         limit = self.model.max_positions
@@ -149,22 +186,22 @@ class Engine:
                 self.admit(e.rid)
             before = alloc.length(e.rid)
             n = len(e.tokens)
-            if limit is not None and before + n > limit:
-                raise StepError(f"request {e.rid!r}: {before + n} tokens exceed the model's {limit} positions")
+            if limit is not None and before + n + extra > limit:
+                raise StepError(f"request {e.rid!r}: {before + n + extra} tokens exceed the model's {limit} positions")
             q_lens.append(n)
             kv_before.append(before)
             slots.append(alloc.slot(e.rid))
-        # all-or-nothing page reservation for the whole step
+        # all-or-nothing page reservation for the whole step (or burst)
         need = [0] * len(alloc.pools)
         for e, n, before in zip(entries, q_lens, kv_before):
-            for g, k in enumerate(alloc.pages_needed(e.rid, before + n)):
+            for g, k in enumerate(alloc.pages_needed(e.rid, before + n + extra)):
                 need[g] += k
         for g, k in enumerate(need):
             if k > alloc.free_pages(g):
                 raise OutOfPages(f"step needs {k} new pages in cache group {g}, "
                                  f"{alloc.free_pages(g)} of {alloc.pools[g].num_pages} are free")
         for e, n, before in zip(entries, q_lens, kv_before):
-            alloc.reserve(e.rid, before + n)
+            alloc.reserve(e.rid, before + n + extra)
 
         T, S = sum(q_lens), len(entries)
         R = sum(len(e.want) for e in entries)
@@ -172,9 +209,12 @@ class Engine:
             raise StepError(f"{len(sampling)} sampling rows for {R} wanted places")
         groups = self.cache.layout.groups
         decode_only = max(q_lens) == 1
-        max_blocks = max(-(-(b + n) // self.cache.page_size) for b, n in zip(kv_before, q_lens))
+        if n_burst and (not decode_only or R != S or sampling is None):
+            raise StepError("a burst takes single tokens only, each with its logits wanted and sampled")
+        page = self.cache.page_size
+        max_blocks = max(-(-(b + n + extra) // page) for b, n in zip(kv_before, q_lens))
         max_blocks = max(8, -(-max_blocks // 8) * 8)      # widths in steps of 8: few distinct graphs
-        n_sample = 4 * R if sampling is not None else 0
+        n_sample = (4 * R if sampling is not None else 0) + (R + n_burst * R if n_burst else 0)
         total = 3 * T + S + (S + 1) + S + R + n_sample + len(groups) * S * max_blocks
         bi = self._staging.acquire(total)
         h = self._staging.host_np[bi]
@@ -194,44 +234,67 @@ class Engine:
         qs_v, qs_s = take(S + 1)
         kvb_v, kvb_s = take(S)
         rows_v, rows_s = take(R)
-        t0, r0 = 0, 0
         vocab = self.vocab_size
-        for s, (e, n, before) in enumerate(zip(entries, q_lens, kv_before)):
-            toks = np.asarray(e.tokens, dtype=np.int64)
-            if toks.min() < 0 or toks.max() >= vocab:
-                raise StepError(f"request {e.rid!r}: a token id is outside the vocabulary of {vocab}")
-            ids_v[t0:t0 + n] = toks
-            pos_v[t0:t0 + n] = np.arange(before, before + n, dtype=np.int32)
-            seq_v[t0:t0 + n] = s
-            qs_v[s] = t0
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise StepError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
-                rows_v[r0] = t0 + int(w)
-                r0 += 1
-            t0 += n
-        qs_v[S] = T
+        if decode_only:
+            ids_v[:] = [e.tokens[0] for e in entries]
+            if int(ids_v.min()) < 0 or int(ids_v.max()) >= vocab:
+                raise StepError(f"a token id is outside the vocabulary of {vocab}")
+            pos_v[:] = kv_before
+            seq_v[:] = np.arange(S, dtype=np.int32)
+            qs_v[:] = np.arange(S + 1, dtype=np.int32)
+            r0 = 0
+            for s, e in enumerate(entries):
+                for w in e.want:
+                    if int(w) != 0:
+                        raise StepError(f"request {e.rid!r}: wanted place {w} is outside its 1 token")
+                    rows_v[r0] = s
+                    r0 += 1
+        else:
+            t0, r0 = 0, 0
+            for s, (e, n, before) in enumerate(zip(entries, q_lens, kv_before)):
+                toks = np.asarray(e.tokens, dtype=np.int64)
+                if toks.min() < 0 or toks.max() >= vocab:
+                    raise StepError(f"request {e.rid!r}: a token id is outside the vocabulary of {vocab}")
+                ids_v[t0:t0 + n] = toks
+                pos_v[t0:t0 + n] = np.arange(before, before + n, dtype=np.int32)
+                seq_v[t0:t0 + n] = s
+                qs_v[s] = t0
+                for w in e.want:
+                    if not (0 <= int(w) < n):
+                        raise StepError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
+                    rows_v[r0] = t0 + int(w)
+                    r0 += 1
+                t0 += n
+            qs_v[S] = T
         slot_v[:] = slots
         kvb_v[:] = kv_before
         sample_s = None
         if sampling is not None:
             sv, sample_s = take(4 * R)
             fv = sv.view(np.float32)
-            for i, row in enumerate(sampling):
-                fv[i] = row.temperature
-                sv[R + i] = row.top_k
-                fv[2 * R + i] = row.top_p
-                fv[3 * R + i] = row.uniform
+            fv[:R] = [row.temperature for row in sampling]
+            sv[R:2 * R] = [row.top_k for row in sampling]
+            fv[2 * R:3 * R] = [row.top_p for row in sampling]
+            fv[3 * R:] = [row.uniform for row in sampling]
+        step_s = None
+        if n_burst:
+            stv, step_s = take(R)
+            stv[:] = 0
         table_slices = {}
         for g in groups:
             tv, ts = take(S * max_blocks)
             tv = tv.reshape(S, max_blocks)
             tv[:] = FREED
             for s, e in enumerate(entries):
-                bl = alloc.block_list(e.rid, g.index)
-                m = min(len(bl), max_blocks)
-                tv[s, :m] = bl[:m]
+                row = self._table_row(e.rid, g.index)
+                m = min(row.shape[0], max_blocks)
+                tv[s, :m] = row[:m]
             table_slices[g.index] = ts
+        uni_s = None
+        if n_burst:
+            # last in the buffer: its length changes with the burst, nothing else may move with it
+            uv, uni_s = take(n_burst * R)
+            uv.view(np.float32)[:] = burst_uniform.reshape(-1)
         self._staging.send(bi, total)
         self.last_h2d_bytes = 4 * total
 
@@ -245,32 +308,36 @@ class Engine:
             block_tables={g: d(sl).view(S, max_blocks) for g, sl in table_slices.items()},
             compute_dtype=self.dtype, workspace=self.workspace, caches=self.cache.device_caches,
             host_q_lens=q_lens, host_kv_before=kv_before, host_slots=slots,
-            max_q_len=max(q_lens), max_kv_len=max(b + n for b, n in zip(kv_before, q_lens)),
+            max_q_len=max(q_lens), max_kv_len=max(b + n for b, n in zip(kv_before, q_lens)) + extra,
         )
         sample_dev = d(sample_s) if sample_s is not None else None
-        key = (T, S, R, max_blocks, sampling is not None, self._staging.generation) if decode_only else None
-        return ctx, sample_dev, key
+        key = (T, S, R, max_blocks, sampling is not None, n_burst > 0, self._staging.generation) \
+            if decode_only else None
+        burst = (d(uni_s).view(torch.float32), d(step_s)) if n_burst else None
+        return _Prepared(ctx, sample_dev, key, burst)
 
-    def _run(self, ctx: StepContext, sample_dev: Optional[torch.Tensor]) -> torch.Tensor:
+    # ---- running it ------------------------------------------------------------------------
+    def _run(self, p: _Prepared) -> torch.Tensor:
+        ctx = p.ctx
         logits = self.model.forward(ctx, status=self._status)
         R = ctx.logit_rows.numel()
-        if sample_dev is not None and R:
-            f = sample_dev.view(torch.float32)
-            ops.sample(logits, self._sampled[:R], temperature=f[:R], top_k=sample_dev[R:2 * R],
-                       top_p=f[2 * R:3 * R], uniform=f[3 * R:4 * R], status=self._status)
+        if p.sample is not None and R:
+            f = p.sample.view(torch.float32)
+            if p.burst is not None:
+                uniform, row_step = p.burst
+                ops.sample(logits, self._sampled[:R], temperature=f[:R], top_k=p.sample[R:2 * R],
+                           top_p=f[2 * R:3 * R], uniform=uniform, status=self._status,
+                           feedback=(ctx.token_ids, ctx.logit_rows, ctx.positions, self._burst_tokens, row_step))
+            else:
+                ops.sample(logits, self._sampled[:R], temperature=f[:R], top_k=p.sample[R:2 * R],
+                           top_p=f[2 * R:3 * R], uniform=f[3 * R:4 * R], status=self._status)
         return logits
 
-    def step(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]] = None,
-             reserved: bool = False) -> torch.Tensor:
-        """Run one step; returns float32 logits [wanted, vocab] on the device.  The tensor is
-        workspace memory: the next step overwrites it.  With `sampling` (one SampleRow per
-        wanted place) the drawn tokens are in `self.sampled_tokens(n)` afterwards."""
-        entries = [e for e in entries if len(e.tokens) > 0]
-        ctx, sample_dev, key = self._prepare(entries, sampling)
-        R = ctx.logit_rows.numel()
-        if self._sampled.numel() < R:
-            self._sampled = torch.zeros(R, dtype=torch.int32, device=self.device)
+    def _execute(self, p: _Prepared, times: int = 1) -> torch.Tensor:
+        """Run the prepared step `times` times (more than once only for a burst, whose sampler
+        moves the step's inputs on), through a recorded graph where there is one."""
         before = ops.LAUNCHES
+        key = p.key
         if key is not None and self.use_cuda_graphs:
             hit = self._graphs.get(key)
             if hit is not None and hit[3] != self.workspace.version:
@@ -280,31 +347,74 @@ class Engine:
                 hit = None
                 self.stale_graphs += 1
             if hit is not None:
-                hit[0].replay()
-                logits = hit[1]
-                self.graph_replays += 1
+                for _ in range(times):
+                    hit[0].replay()
+                self.graph_replays += times
                 self.last_launches = hit[2]
-            elif self._seen.get(key, 0) >= 1:
+                return hit[1]
+            if self._seen.get(key, 0) >= 1:
                 # the second time a shape comes by it is recorded; the record is then run
                 torch.cuda.current_stream().synchronize()
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
-                    logits = self._run(ctx, sample_dev)
+                    logits = self._run(p)
                 n_launch = ops.LAUNCHES - before
                 self._graphs[key] = (graph, logits, n_launch, self.workspace.version)
-                graph.replay()
+                for _ in range(times):
+                    graph.replay()
                 self.last_launches = n_launch
-            else:
-                self._seen[key] = 1
-                logits = self._run(ctx, sample_dev)
-                self.last_launches = ops.LAUNCHES - before
-        else:
-            logits = self._run(ctx, sample_dev)
-            self.last_launches = ops.LAUNCHES - before
-        for e, n, b in zip(entries, ctx.host_q_lens, ctx.host_kv_before):
+                return logits
+            self._seen[key] = 1
+        logits = None
+        for _ in range(times):
+            logits = self._run(p)
+        self.last_launches = (ops.LAUNCHES - before) // times
+        return logits
+
+    def step(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]] = None,
+             reserved: bool = False) -> torch.Tensor:
+        """Run one step; returns float32 logits [wanted, vocab] on the device.  The tensor is
+        workspace memory: the next step overwrites it.  With `sampling` (one SampleRow per
+        wanted place) the drawn tokens are in `self.sampled_tokens(n)` afterwards."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        p = self._prepare(entries, sampling)
+        R = p.ctx.logit_rows.numel()
+        if self._sampled.numel() < R:
+            self._sampled = torch.zeros(R, dtype=torch.int32, device=self.device)
+        logits = self._execute(p)
+        for e, n, b in zip(entries, p.ctx.host_q_lens, p.ctx.host_kv_before):
             self.cache.alloc.commit(e.rid, b + n)
         self.steps_run += 1
         return logits
+
+    def decode_burst(self, entries: Sequence[StepEntry], sampling: Sequence[SampleRow],
+                     uniforms: np.ndarray) -> np.ndarray:
+        """Run `n = uniforms.shape[0]` decode steps of the same requests back to back on the
+        device.  Every entry brings one token and wants its logits; step j of request r is drawn
+        with sampling[r] and the uniform number uniforms[j, r]; the token drawn in step j is the
+        input of step j + 1.  Returns the drawn tokens, int32 [n, requests], on the host.
+
+        Pages for all n steps are reserved before anything runs (OutOfPages otherwise, with
+        nothing taken).  The requests' lengths are NOT advanced here: the caller commits as many
+        of each request's steps as it keeps (`commit`), since a request may have hit a stop token
+        part of the way through; what the later steps wrote for it lies beyond its length and is
+        never read."""
+        n = int(uniforms.shape[0])
+        S = len(entries)
+        if not (1 <= n <= MAX_BURST):
+            raise StepError(f"a burst runs 1 to {MAX_BURST} steps, got {n}")
+        if self._burst_tokens.numel() < n * S:
+            raise StepError("more requests in a burst than the engine was built for")
+        p = self._prepare(entries, sampling, burst_uniform=np.ascontiguousarray(uniforms, dtype=np.float32))
+        self._execute(p, times=n)
+        self._burst_host[:n * S].copy_(self._burst_tokens[:n * S], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.steps_run += n
+        return self._burst_host[:n * S].numpy().reshape(n, S).copy()
+
+    def commit(self, rid: Hashable, new_len: int) -> None:
+        """Advance a request's length after a burst (see decode_burst)."""
+        self.cache.alloc.commit(rid, new_len)
 
     def sampled_tokens(self, n: int) -> torch.Tensor:
         """The tokens drawn by the last step with `sampling` (int32 [n] on the device)."""

@@ -156,3 +156,29 @@ def test_on_token_callback_can_cancel(model_dirs):
     r = llm.generate([5, 6, 7], max_tokens=50, on_token=cb)[0]
     assert r.finish_reason == "cancelled" and len(r.output_ids) == 3 == len(seen)
     assert llm.engine.cache.alloc.free_slots() == 8      # everything was given back
+
+
+def test_bursts_give_the_same_tokens_as_single_steps(model_dirs):
+    """Several decode steps per look of the host (tokens fed back on the device) against one
+    step per look: same tokens, same finish reasons, also when a request stops part of the way
+    through a burst and when pages are tight."""
+    prompts = _prompts("B", [3, 40, 17, 64], seed=31)
+    for kw in (dict(max_tokens=37), dict(max_tokens=45, temperature=0.9, seed=5), dict(max_tokens=30, temperature=0.7, top_k=20, top_p=0.9, seed=9)):
+        single = _llm(model_dirs["B"], max_burst=1).generate(prompts, **kw)
+        burst_llm = _llm(model_dirs["B"], max_burst=8)
+        burst = burst_llm.generate(prompts, **kw)
+        assert [r.output_ids for r in burst] == [r.output_ids for r in single]
+        assert [r.finish_reason for r in burst] == [r.finish_reason for r in single]
+        assert burst_llm.engine.graph_replays > 0
+    # a stop token in the middle of a burst: the tokens after it are dropped
+    free = _llm(model_dirs["B"], max_burst=1).generate(prompts[1], max_tokens=40)[0].output_ids
+    stop = free[13]
+    cut = free.index(stop)
+    r = _llm(model_dirs["B"], max_burst=8).generate(prompts[1], max_tokens=40, stop_token_ids=[stop])[0]
+    assert r.output_ids == free[:cut + 1] and r.finish_reason == "stop"
+    # tight pages: bursts shrink instead of failing, preemption still works
+    tight = _llm(model_dirs["B"], cache_tokens=224, page_size=16, max_burst=8)
+    roomy = _llm(model_dirs["B"], cache_tokens=4096, max_burst=1)
+    kw = dict(max_tokens=50)
+    assert [r.output_ids for r in tight.generate(prompts, **kw)] == [r.output_ids for r in roomy.generate(prompts, **kw)]
+    tight.engine.cache.alloc.check()
