@@ -40,6 +40,7 @@ from ..models.model import Model
 from ..parts.base import StepContext, Workspace
 
 MAX_BURST = 32      # most decode steps one decode_burst may run
+MAX_GRAPHS = 64     # most recorded step shapes kept at a time
 
 
 @dataclasses.dataclass
@@ -311,8 +312,10 @@ class Engine:
             max_q_len=max(q_lens), max_kv_len=max(b + n for b, n in zip(kv_before, q_lens)) + extra,
         )
         sample_dev = d(sample_s) if sample_s is not None else None
-        key = (T, S, R, max_blocks, sampling is not None, n_burst > 0, self._staging.generation) \
-            if decode_only else None
+        # Everything a launch's shape depends on.  The portions' own lengths and starts are device
+        # data (q_start, kv_before, positions), so steps that agree on these counts share a graph:
+        # decode steps always do, prompt steps do when the token budget is filled the same way.
+        key = (T, S, R, max(q_lens), max_blocks, sampling is not None, n_burst > 0, self._staging.generation)
         burst = (d(uni_s).view(torch.float32), d(step_s)) if n_burst else None
         return _Prepared(ctx, sample_dev, key, burst)
 
@@ -359,6 +362,8 @@ class Engine:
                 with torch.cuda.graph(graph):
                     logits = self._run(p)
                 n_launch = ops.LAUNCHES - before
+                while len(self._graphs) >= MAX_GRAPHS:          # the oldest recording makes room
+                    del self._graphs[next(iter(self._graphs))]
                 self._graphs[key] = (graph, logits, n_launch, self.workspace.version)
                 for _ in range(times):
                     graph.replay()
