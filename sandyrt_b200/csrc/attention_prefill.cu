@@ -7,13 +7,20 @@
 // tokens of one (request, head); Q.K^T and P.V run as warp-level matrix instructions
 // (mma.sync m16n8k16, bfloat16 in, float accumulate), the softmax is the online form carried
 // in float registers, and key/value tiles of 64 positions stream from the request's pages
-// into shared memory with cp.async, double-buffered.
+// into shared memory with cp.async through a ring of three buffers (one block-wide barrier per
+// tile).  The request's row of the block table is copied to shared memory once, so finding a
+// key's page costs no trip to global memory inside the loop.
 //
 // Like every attention kernel here it reads all keys from the cache (the step's own keys are
 // appended first), the prefix a request already had and the portion it brings alike, so a
 // portion that starts in the middle of a prompt needs nothing special: query i of the
 // portion sits at position kv_before + i and sees keys max(0, pos+1-window) .. pos.
 // A request that brings a single token is just a tile with one live row.
+//
+// A block has eight warps: four row groups of 16 queries, each served by two warps that take
+// one half of every key tile (32 keys) and keep their own running (max, sum, output); the two
+// halves are merged through shared memory at the end.  This doubles the warps that work on a
+// tile's chain of dependent steps, which is what bounds a causal block with many key tiles.
 //
 // P is rounded to bfloat16 for the P.V product (the row sum is taken before rounding).
 // Head sizes: multiples of 16 up to 128.  Larger heads, and float32, use the general kernel.
@@ -23,7 +30,11 @@ namespace {
 
 constexpr int BM = 64;          // queries per block (16 per warp)
 constexpr int BN = 64;          // keys per tile
-constexpr int THREADS = 128;
+constexpr int KSPLIT = 2;        // warp groups that share a query tile and split each key tile between them
+constexpr int BNW = BN / KSPLIT; // keys of a tile one warp works on
+constexpr int THREADS = 128 * KSPLIT;
+constexpr int STAGES = 3;       // key/value tiles in flight
+constexpr int TABLE_SMEM = 1024; // block-table entries kept in shared memory (longer rows are read from global)
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -78,8 +89,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
     constexpr int DTILES = D / 8;            // 8-wide column tiles of the output
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
-    bf16* sK = sQ + BM * LDS;                // [2][BN][LDS]
-    bf16* sV = sK + 2 * BN * LDS;            // [2][BN][LDS]
+    bf16* sK = sQ + BM * LDS;                // [STAGES][BN][LDS]
+    bf16* sV = sK + STAGES * BN * LDS;       // [STAGES][BN][LDS]
+    __shared__ int s_table[TABLE_SMEM];
 
     const int s = blockIdx.z, h = blockIdx.y;
     const int qs = q_start[s];
@@ -98,6 +110,13 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
     const int* table = block_table + (size_t)s * max_blocks;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int page_shift = __ffs(page_size) - 1, page_mask = page_size - 1;      // a power of two
+    const int blocks_used = min(max_blocks, (pos_last >> page_shift) + 1);
+    const bool table_staged = blocks_used <= TABLE_SMEM;
+    if (table_staged) {
+        for (int i = tid; i < blocks_used; i += THREADS) s_table[i] = table[i];
+        __syncthreads();
+    }
 
     // ---- Q tile -------------------------------------------------------------------------
     for (int idx = tid; idx < BM * CHUNKS; idx += THREADS) {
@@ -115,14 +134,14 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
             bool ok = j <= pos_last;
             size_t off = 0;
             if (ok) {
-                const int b = j / page_size;
-                const int page = b < max_blocks ? table[b] : -1;
+                const int b = j >> page_shift;
+                const int page = b < max_blocks ? (table_staged ? s_table[b] : table[b]) : -1;
                 if (page < 0 || page >= num_pages) {
                     // a key with no page behind it; inside the visible range this is a fault
                     if (j >= key_lo && status && c == 0) atomicOr(status, 16);
                     ok = false;
                 } else {
-                    off = (size_t)page * page_stride + ((size_t)kvh * page_size + (j % page_size)) * D + c * 8;
+                    off = (size_t)page * page_stride + ((size_t)kvh * page_size + (j & page_mask)) * D + c * 8;
                 }
             }
             cp_async16(dk + r * LDS + c * 8, k_cache + off, ok ? 16 : 0);
@@ -130,6 +149,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
         }
     };
     load_kv(kt_begin, 0);
+    cp_async_commit();
+    if (kt_begin < kt_end) load_kv(kt_begin + 1, 1);
     cp_async_commit();
 
     float o[DTILES][4];
@@ -140,7 +161,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     const float scale_log2 = scale * 1.4426950408889634f;
     // positions of this thread's two rows (g and g+8 of the warp's 16)
-    const int row0 = warp * 16 + g, row1 = row0 + 8;
+    const int rgroup = warp & 3, khalf = warp >> 2;          // which 16 rows, which half of each key tile
+    const int row0 = rgroup * 16 + g, row1 = row0 + 8;
     const int pos0 = pos_first + row0, pos1 = pos_first + row1;
     const int lo0 = window > 0 ? max(0, pos0 + 1 - window) : 0;
     const int lo1 = window > 0 ? max(0, pos1 + 1 - window) : 0;
@@ -149,30 +171,30 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
     bool q_loaded = false;
 
     for (int kt = kt_begin; kt <= kt_end; kt++) {
-        const int buf = (kt - kt_begin) & 1;
-        if (kt < kt_end) load_kv(kt + 1, buf ^ 1);
+        const int buf = (kt - kt_begin) % STAGES;
+        cp_async_wait<1>();          // tile kt has landed (tile kt+1 may still be on its way)
+        __syncthreads();             // ... for everyone; and everyone is done with tile kt-1
+        if (kt + 2 <= kt_end) load_kv(kt + 2, (kt + 2 - kt_begin) % STAGES);     // into tile kt-1's buffer
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
         if (!q_loaded) {
 #pragma unroll
             for (int kk = 0; kk < KSTEPS; kk++)
-                ldmatrix_x4(qa[kk], sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 16 + (lane >> 4) * 8);
+                ldmatrix_x4(qa[kk], sQ + (rgroup * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 16 + (lane >> 4) * 8);
             q_loaded = true;
         }
-        const bf16* tk = sK + buf * BN * LDS;
-        const bf16* tv = sV + buf * BN * LDS;
+        const bf16* tk = sK + (buf * BN + khalf * BNW) * LDS;      // this warp's half of the tile
+        const bf16* tv = sV + (buf * BN + khalf * BNW) * LDS;
 
-        // ---- S = Q K^T : 16 x 64 per warp ------------------------------------------------
-        float sc[BN / 8][4];
+        // ---- S = Q K^T : 16 x 32 per warp ------------------------------------------------
+        float sc[BNW / 8][4];
 #pragma unroll
-        for (int i = 0; i < BN / 8; i++)
+        for (int i = 0; i < BNW / 8; i++)
 #pragma unroll
             for (int j = 0; j < 4; j++) sc[i][j] = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; kk++) {
 #pragma unroll
-            for (int nt = 0; nt < BN / 8; nt += 2) {
+            for (int nt = 0; nt < BNW / 8; nt += 2) {
                 uint32_t kb[4];
                 ldmatrix_x4(kb, tk + (nt * 8 + (lane & 7) + (lane >> 4) * 8) * LDS + kk * 16 + ((lane >> 3) & 1) * 8);
                 mma_bf16(sc[nt], qa[kk], kb[0], kb[1]);
@@ -181,14 +203,22 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
         }
         // ---- mask, online softmax --------------------------------------------------------
         float m_new[2] = {m_run[0], m_run[1]};
+        // a tile every row of the block sees whole needs no mask (all tiles but the last one
+        // or two of a causal block, when there is no window)
+        const bool whole = kt * BN + BN - 1 <= pos_first && (window == 0 || kt * BN >= pos_last + 1 - window);
 #pragma unroll
-        for (int nt = 0; nt < BN / 8; nt++) {
-            const int j0 = kt * BN + nt * 8 + 2 * t;
+        for (int nt = 0; nt < BNW / 8; nt++) {
+            if (whole) {
 #pragma unroll
-            for (int e = 0; e < 2; e++) {
-                const int j = j0 + e;
-                sc[nt][e] = (j <= pos0 && j >= lo0) ? sc[nt][e] * scale_log2 : -INFINITY;
-                sc[nt][2 + e] = (j <= pos1 && j >= lo1) ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+                for (int e = 0; e < 4; e++) sc[nt][e] *= scale_log2;
+            } else {
+                const int j0 = kt * BN + khalf * BNW + nt * 8 + 2 * t;
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int j = j0 + e;
+                    sc[nt][e] = (j <= pos0 && j >= lo0) ? sc[nt][e] * scale_log2 : -INFINITY;
+                    sc[nt][2 + e] = (j <= pos1 && j >= lo1) ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+                }
             }
             m_new[0] = fmaxf(m_new[0], fmaxf(sc[nt][0], sc[nt][1]));
             m_new[1] = fmaxf(m_new[1], fmaxf(sc[nt][2], sc[nt][3]));
@@ -206,9 +236,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
             m_run[r] = m_new[r];
         }
         float l_add[2] = {0.0f, 0.0f};
-        uint32_t pa[BN / 16][4];
+        uint32_t pa[BNW / 16][4];
 #pragma unroll
-        for (int nt = 0; nt < BN / 8; nt++) {
+        for (int nt = 0; nt < BNW / 8; nt++) {
             const float p0 = exp2f(sc[nt][0] - msafe[0]), p1 = exp2f(sc[nt][1] - msafe[0]);
             const float p2 = exp2f(sc[nt][2] - msafe[1]), p3 = exp2f(sc[nt][3] - msafe[1]);
             l_add[0] += p0 + p1;
@@ -230,7 +260,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
         }
         // ---- O += P V --------------------------------------------------------------------
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; kk++) {
+        for (int kk = 0; kk < BNW / 16; kk++) {
 #pragma unroll
             for (int dt = 0; dt < DTILES; dt += 2) {
                 uint32_t vb[4];
@@ -239,9 +269,40 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
                 mma_bf16(o[dt + 1], pa[kk], vb[2], vb[3]);
             }
         }
-        __syncthreads();      // everyone is done with this buffer before the next load lands in it
     }
     cp_async_wait<0>();
+
+    // ---- merge the two key halves of every row group (the tile buffers are free now) ------
+    __syncthreads();
+    float* mrg = reinterpret_cast<float*>(sK);               // [4 row groups][32 lanes][DTILES*4 + 4]
+    constexpr int MRG = DTILES * 4 + 4;
+    if (khalf == 1) {
+        float* dst = mrg + (size_t)(rgroup * 32 + lane) * MRG;
+#pragma unroll
+        for (int dt = 0; dt < DTILES; dt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) dst[dt * 4 + e] = o[dt][e];
+        dst[DTILES * 4 + 0] = m_run[0]; dst[DTILES * 4 + 1] = m_run[1];
+        dst[DTILES * 4 + 2] = l_run[0]; dst[DTILES * 4 + 3] = l_run[1];
+    }
+    __syncthreads();
+    if (khalf == 1) return;
+    {
+        const float* src = mrg + (size_t)(rgroup * 32 + lane) * MRG;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const float m_o = src[DTILES * 4 + r], l_o = src[DTILES * 4 + 2 + r];
+            const float m_all = fmaxf(m_run[r], m_o);
+            const float msafe = m_all == -INFINITY ? 0.0f : m_all;
+            const float wa = exp2f(m_run[r] - msafe), wb = exp2f(m_o - msafe);
+            l_run[r] = l_run[r] * wa + l_o * wb;
+#pragma unroll
+            for (int dt = 0; dt < DTILES; dt++) {
+                o[dt][2 * r] = o[dt][2 * r] * wa + src[dt * 4 + 2 * r] * wb;
+                o[dt][2 * r + 1] = o[dt][2 * r + 1] * wa + src[dt * 4 + 2 * r + 1] * wb;
+            }
+        }
+    }
 
     // ---- write back ----------------------------------------------------------------------
     const float inv0 = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f;
@@ -264,7 +325,7 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
            int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int page_size, float scale, int window,
            int num_pages, int* status, cudaStream_t stream) {
     constexpr int LDS = D + 8;
-    const int smem = (BM + 4 * BN) * LDS * (int)sizeof(bf16);
+    const int smem = (BM + 2 * STAGES * BN) * LDS * (int)sizeof(bf16);
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -291,6 +352,7 @@ SANDY_API int sandy_prefill_attention(const void* q, int ld_q, const void* k_cac
     if (n_seqs == 0 || max_q_len == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !q_start || !kv_before || !out) return SANDY_ERR_ARGUMENT;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0) return SANDY_ERR_UNSUPPORTED;
+    if (page_size & (page_size - 1)) return SANDY_ERR_UNSUPPORTED;      // pages are a power of two long
     if (n_heads > 65535 || n_seqs > 65535) return SANDY_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
         (reinterpret_cast<uintptr_t>(v_cache) & 15) || (reinterpret_cast<uintptr_t>(out) & 3))

@@ -4,18 +4,74 @@
 // twin src/device/cuda/CudaNormKernels.cu:172-206):
 //   mean = sum(x) / E;  var = sum((x - mean)^2) / E   (biased, two passes)
 //   y = (x - mean) * (1 / sqrt(var + eps)) * gamma + beta
-// The reference reads the row from global memory three times; here the row is staged in
-// shared memory once as floats and all three passes read that copy.
+// The reference gives every row a block of 256 threads and reads the row from global memory
+// three times.  Here a row belongs to ONE WARP and lives in its registers between the passes
+// (rows up to 4096 wide; wider rows take the block-per-row kernel that stages the row in
+// shared memory), so the two reductions are warp shuffles and a block handles eight rows.
 //
 // `rows` (optional) selects which input rows are normalised: output row r is the norm of
 // input row rows[r].  The engine uses it to run the final norm only at the positions
 // whose logits were asked for.
 #include "common.cuh"
 
+namespace {
+
+constexpr int ROWS_PER_BLOCK = 8;
+
+// VEC: elements per lane per round (4 floats or 8 halfs = 16 bytes); NV: rounds (width <= 32*4*NV)
+template <typename TI, typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
+layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, const TW* __restrict__ beta,
+                      TO* __restrict__ out, const int* __restrict__ rows, int n_rows, int width, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * ROWS_PER_BLOCK + warp;
+    if (r >= n_rows) return;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    const TI* xr = x + src * width;
+    float v[NV][4];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const int e = (i * 32 + lane) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            v[i][j] = (e + j < width) ? to_f32(xr[e + j]) : 0.0f;
+            s += v[i][j];
+        }
+    }
+    const float mean = warp_sum(s) / (float)width;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const int e = (i * 32 + lane) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float c = v[i][j] - mean;
+            if (e + j < width) q += c * c;
+        }
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)width + eps);
+    TO* orow = out + (size_t)r * width;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const int e = (i * 32 + lane) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            if (e + j < width) {
+                float y = (v[i][j] - mean) * inv * to_f32(gamma[e + j]);
+                if (beta) y += to_f32(beta[e + j]);
+                orow[e + j] = from_f32<TO>(y);
+            }
+        }
+    }
+}
+
 template <typename TI, typename TW, typename TO>
-__global__ void layernorm_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma,
-                                 const TW* __restrict__ beta, TO* __restrict__ out,
-                                 const int* __restrict__ rows, int width, float eps) {
+__global__ void layernorm_block_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma,
+                                       const TW* __restrict__ beta, TO* __restrict__ out,
+                                       const int* __restrict__ rows, int width, float eps) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -45,6 +101,29 @@ __global__ void layernorm_kernel(const TI* __restrict__ x, const TW* __restrict_
     }
 }
 
+template <typename TI, typename TW, typename TO>
+int launch(const void* x, const void* gamma, const void* beta, void* out, const int* rows, int n_rows, int width,
+           float eps, cudaStream_t stream) {
+    const dim3 grid((n_rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), block(ROWS_PER_BLOCK * 32);
+#define WARP_CASE(NV)                                                                                          \
+    if (width <= 128 * NV)                                                                                     \
+        return sandy_launch(layernorm_warp_kernel<TI, TW, TO, NV>, grid, block, 0, stream, (const TI*)x,       \
+                            (const TW*)gamma, (const TW*)beta, (TO*)out, rows, n_rows, width, eps)
+    WARP_CASE(1); WARP_CASE(2); WARP_CASE(4); WARP_CASE(8); WARP_CASE(16); WARP_CASE(32);
+#undef WARP_CASE
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return SANDY_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(layernorm_block_kernel<TI, TW, TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return sandy_launch(layernorm_block_kernel<TI, TW, TO>, dim3(n_rows), dim3(512), smem, stream, (const TI*)x,
+                        (const TW*)gamma, (const TW*)beta, (TO*)out, rows, width, eps);
+}
+
+}  // namespace
+
 // x: [*, width] of in_dtype; gamma, beta: [width] of w_dtype (beta may be null);
 // out: [n_rows, width] of out_dtype; rows: int32[n_rows] or null.
 SANDY_API int sandy_layernorm(const void* x, const void* gamma, const void* beta, void* out,
@@ -52,21 +131,13 @@ SANDY_API int sandy_layernorm(const void* x, const void* gamma, const void* beta
                               int in_dtype, int w_dtype, int out_dtype, cudaStream_t stream) {
     if (n_rows == 0) return SANDY_OK;
     if (!x || !gamma || !out || width <= 0) return SANDY_ERR_ARGUMENT;
-    const size_t smem = (size_t)width * sizeof(float);
-    if (smem > 200 * 1024) return SANDY_ERR_UNSUPPORTED;
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-#define LAUNCH(TI, TW, TO)                                                                      \
-    do {                                                                                        \
-        if (smem > 48 * 1024)                                                                   \
-            cudaFuncSetAttribute(layernorm_kernel<TI, TW, TO>,                                  \
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        return sandy_launch(layernorm_kernel<TI, TW, TO>, dim3(n_rows), dim3(threads), smem, stream, \
-                            (const TI*)x, (const TW*)gamma, (const TW*)beta, (TO*)out, rows, width, eps); \
-    } while (0)
-    if (in_dtype == SANDY_F32 && w_dtype == SANDY_F32 && out_dtype == SANDY_F32) LAUNCH(float, float, float);
-    if (in_dtype == SANDY_F32 && w_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) LAUNCH(float, bf16, bf16);
-    if (in_dtype == SANDY_BF16 && w_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) LAUNCH(bf16, bf16, bf16);
-    if (in_dtype == SANDY_F32 && w_dtype == SANDY_F32 && out_dtype == SANDY_BF16) LAUNCH(float, float, bf16);
-#undef LAUNCH
+#define CASE(DI, DW, DO, TI, TW, TO)                                                                 \
+    if (in_dtype == DI && w_dtype == DW && out_dtype == DO)                                          \
+        return launch<TI, TW, TO>(x, gamma, beta, out, rows, n_rows, width, eps, stream)
+    CASE(SANDY_F32, SANDY_F32, SANDY_F32, float, float, float);
+    CASE(SANDY_F32, SANDY_BF16, SANDY_BF16, float, bf16, bf16);
+    CASE(SANDY_BF16, SANDY_BF16, SANDY_BF16, bf16, bf16, bf16);
+    CASE(SANDY_F32, SANDY_F32, SANDY_BF16, float, float, bf16);
+#undef CASE
     return SANDY_ERR_UNSUPPORTED;
 }
