@@ -40,6 +40,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_skinny": [],
     "attention": [],
     "attention_decode": [],
+    "attention_decode_bulk": [],
     "attention_prefill": [],
     "sampling": [],
 }

@@ -9,6 +9,7 @@ library cannot be built or loaded, the call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -206,13 +207,23 @@ def decode_splits(n_tokens: int, n_heads: int, max_kv: int) -> int:
 
 
 CLUSTER_MAX_SPLITS = 8
+# From this many (token, head) pairs on, a decode step's attention streams pages through shared
+# memory with bulk copies (attention_decode_bulk.cu) instead of through registers.  Measured on
+# GPT-2 small's shape: 64 x 12 pairs of 384 keys, cache read from HBM, 18.8 against 45.5 us a
+# layer; but a whole decode step of 8 x 12 pairs (its cache fits in L2) took 414 against 400 us
+# and one of 1 x 12 pairs 356 against 333 us, the register kernel starting sooner.
+BULK_MIN_PAIRS = 256
+_BULK_MODE = os.environ.get("SANDYRT_DECODE_BULK", "auto")     # "0" / "1" force one kernel, for comparisons
 
 
 def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int,
-                     scale: float, window: int = 0, num_splits: int = 1, scratch=None, cluster: bool = False) -> None:
+                     scale: float, window: int = 0, num_splits: int = 1, scratch=None, cluster: bool = False,
+                     bulk: bool = False) -> None:
     """Split-KV attention of single tokens (head sizes 16/32/64/128, 256 in bfloat16).  With
     `cluster` (2..8 splits) the splits merge through distributed shared memory inside one
-    kernel; otherwise they go through `scratch` and a merge kernel."""
+    kernel; otherwise they go through `scratch` and a merge kernel.  `bulk` (at most 8 splits)
+    runs the variant that streams whole pages into shared memory with bulk copies, which is
+    the faster one when there are hundreds of (token, head) pairs."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, scratch)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -224,6 +235,18 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
             or q.dtype != k_cache.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
     _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
+    if bulk:
+        if num_splits > CLUSTER_MAX_SPLITS:
+            raise UnsupportedShape(f"decode_attention: a cluster holds at most {CLUSTER_MAX_SPLITS} splits")
+        lib = load_library("attention_decode_bulk")
+        code = lib.sandy_decode_attention_bulk(
+            _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride),
+            _p(block_table), ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
+            ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d),
+            ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_splits),
+            ctypes.c_int(num_pages), ctypes.c_int(_dt(q)), _p(kernel_status(q.device)), _stream())
+        _check(code, f"decode_attention_bulk(H={n_heads},Hkv={hkv},D={d},page={ps},splits={num_splits})")
+        return
     if cluster and num_splits > 1:
         if num_splits > CLUSTER_MAX_SPLITS:
             raise UnsupportedShape(f"decode_attention: a cluster holds at most {CLUSTER_MAX_SPLITS} splits")
@@ -292,8 +315,11 @@ def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale
     if ctx.max_q_len == 1 and d in _DECODE_HEAD_DIMS.get(q.dtype, ()):
         max_kv = block_table.shape[1] * k_cache.shape[2]
         splits = min(decode_splits(ctx.n_tokens, n_heads, max_kv), CLUSTER_MAX_SPLITS)
+        stage = 2 * k_cache.shape[2] * d * q.element_size()
+        fits = stage * 4 <= 160 * 1024          # the ring holds at least four stages
+        bulk = fits and (ctx.n_tokens * n_heads >= BULK_MIN_PAIRS if _BULK_MODE == "auto" else _BULK_MODE == "1")
         decode_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out, n_heads=n_heads,
-                         scale=scale, window=window, num_splits=splits, cluster=True)
+                         scale=scale, window=window, num_splits=splits, cluster=True, bulk=bulk)
         return
     paged_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out,
                     n_heads=n_heads, scale=scale, window=window)

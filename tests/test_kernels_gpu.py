@@ -275,7 +275,28 @@ def test_decode_attention_split_kv(dtype, H, Hkv, D, page_size, window, splits):
         assert torch.equal(out2, out)
 
 
-@pytest.mark.parametrize("kernel", ["general", "decode"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,D,page_size,window", [(4, 4, 16, 16, 0), (3, 3, 32, 64, 0), (12, 12, 64, 16, 0),
+                                                     (6, 2, 64, 8, 0), (4, 1, 128, 32, 0), (5, 5, 64, 16, 100),
+                                                     (2, 2, 32, 128, 0), (3, 1, 32, 4, 9)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_decode_attention_bulk(dtype, H, Hkv, D, page_size, window, splits):
+    """The variant that streams pages through a shared-memory ring: contexts of 1 to 700 keys
+    (more pages than the ring has stages, so stages are used again), splits at page edges."""
+    from sandyrt_b200.csrc import ops
+
+    seqs = [(699, 1), (0, 1), (63, 1), (64, 1), (300, 1), (15, 1), (128, 1)]
+    case = _paged_case(dtype, H, Hkv, D, page_size, seqs, seed=D + splits)
+    out = torch.full_like(case["q"], float("nan"))
+    scale = 1.0 / math.sqrt(D)
+    ops.decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"], out,
+                         n_heads=H, scale=scale, window=window, num_splits=splits, bulk=True)
+    ops.check_kernel_status(DEV)
+    want = _attention_want(case, H, Hkv, D, scale, window)
+    assert (out.double().cpu() - want).abs().max().item() < ATT_TOL[dtype]
+
+
+@pytest.mark.parametrize("kernel", ["general", "decode", "bulk"])
 def test_one_far_key_among_hundreds(kernel):
     """Scale one query/key pair so that a single score dominates: a kernel that dropped or
     misplaced that key (a page's edge, a split's edge) returns a visibly different output."""
@@ -290,6 +311,9 @@ def test_one_far_key_among_hundreds(kernel):
         if kernel == "general":
             ops.paged_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"],
                                 out, n_heads=H, scale=0.125)
+        elif kernel == "bulk":
+            ops.decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"],
+                                 out, n_heads=H, scale=0.125, num_splits=7, bulk=True)
         else:
             scratch = torch.empty(2 * H * 7 * (D + 2), dtype=torch.float32, device=DEV)
             ops.decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"],
