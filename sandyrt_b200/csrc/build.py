@@ -41,6 +41,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention": [],
     "attention_decode": [],
     "attention_decode_bulk": [],
+    "decode_program": [],
     "attention_prefill": [],
     "sampling": [],
 }

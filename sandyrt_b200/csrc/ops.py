@@ -49,6 +49,16 @@ def _stream():
 # Number of kernel launches issued through this module (benchmarks report it).
 LAUNCHES = 0
 
+# While a decode program is being recorded (program.recording) the functions a decode step uses
+# append a record to it instead of launching; every other function refuses.
+_recorder = None
+
+
+def _no_record(what: str) -> None:
+    if _recorder is not None:
+        from .program import NotRecordable
+        raise NotRecordable(what)
+
 
 def _check(code: int, what: str) -> None:
     global LAUNCHES
@@ -85,6 +95,8 @@ def embed_positions(ids, positions, wte, wpe, out, status=None) -> None:
             raise KernelError("position table must match the token table in dtype and width")
     if wte.shape[1] != width or not (wte.is_contiguous() and out.is_contiguous()):
         raise KernelError("embed_positions: tables and output must be contiguous and of one width")
+    if _recorder is not None:
+        return _recorder.embed(ids, positions, wte, wpe, out, status)
     lib = load_library("embed")
     code = lib.sandy_embed_pos(_p(ids), _p(positions), _p(wte), _p(wpe), _p(out),
                                ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(wte.shape[0]),
@@ -106,6 +118,8 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
         raise KernelError("layernorm: x and out disagree")
     if not (x.is_contiguous() and out.is_contiguous()) or out.shape[-1] != width or gamma.numel() != width:
         raise KernelError("layernorm: contiguous [rows, width] tensors expected")
+    if _recorder is not None:
+        return _recorder.norm(x, gamma, beta, eps, out, rows)
     lib = load_library("norm")
     code = lib.sandy_layernorm(_p(x), _p(gamma), _p(beta), _p(out), _p(rows), ctypes.c_int(n_rows),
                                ctypes.c_int(width), ctypes.c_float(eps), ctypes.c_int(_dt(x)),
@@ -115,6 +129,7 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
 
 def gemm_simt(a, w, bias, out, *, w_out_in: bool, act=None, residual=None) -> None:
     """out = act(a @ W + bias) + residual on the 32-bit pipes.  W is [K,N], or [N,K] with w_out_in."""
+    _no_record("a float32 product")
     _cuda(a, w, bias, out, residual)
     M, K = a.shape
     N = out.shape[1]
@@ -153,6 +168,7 @@ def _cache_args(k_cache, v_cache):
 
 def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions) -> None:
     """Write the step's keys/values ([T, Hkv*D] views, one row stride) into their pages."""
+    _no_record("a separate key/value write")
     _cuda(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = k_src.shape[0]
@@ -172,6 +188,7 @@ def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
 def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *,
                     n_heads: int, scale: float, window: int = 0) -> None:
     """Causal attention of every token of the step over its request's pages (general kernel)."""
+    _no_record("the general attention kernel")
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -224,6 +241,7 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
     kernel; otherwise they go through `scratch` and a merge kernel.  `bulk` (at most 8 splits)
     runs the variant that streams whole pages into shared memory with bulk copies, which is
     the faster one when there are hundreds of (token, head) pairs."""
+    _no_record("a decode attention kernel called by name")
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, scratch)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -281,6 +299,7 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
                       max_q_len: int, scale: float, window: int = 0) -> None:
     """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).
     q_start: int32 [S+1] first new token of each request; kv_before: int32 [S]."""
+    _no_record("attention of prompt portions")
     _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     if q.dtype != torch.bfloat16 or d % 16 != 0 or d > 128:
@@ -308,6 +327,14 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
 def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale: float, window: int = 0) -> None:
     """Attention of a step's tokens over the cache: picks the kernel for the step's shape."""
     d = k_cache.shape[3]
+    if _recorder is not None:
+        if ctx.max_q_len != 1:
+            _no_record("attention of prompt portions")
+        hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
+        _i32(block_table, "block_table")
+        return _recorder.attention(q, k_cache, v_cache, page_stride, num_pages, block_table, ctx.token_seq,
+                                   ctx.positions, out, n_heads=n_heads, n_kv_heads=hkv, head_dim=d, page_size=ps,
+                                   scale=scale, window=window)
     if ctx.max_q_len > 1 and q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 128:
         prefill_attention(q, k_cache, v_cache, block_table, ctx.q_start, ctx.kv_before, out, n_heads=n_heads,
                           max_q_len=ctx.max_q_len, scale=scale, window=window)
@@ -331,6 +358,7 @@ def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, unif
     feedback: (token_ids, logit_rows, positions, burst_tokens, row_step) int32 device tensors: the
     drawn token also replaces the row's input token, its position moves on, and the token is
     recorded in burst_tokens[row_step[r], r]; `uniform` then holds [steps, rows] numbers."""
+    _no_record("sampling")
     _cuda(logits, out_tokens, temperature, top_k, top_p, uniform, status)
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 with unit inner stride")
@@ -379,9 +407,12 @@ def check_kernel_status(device) -> None:
     code = int(t.item())
     if code:
         t.zero_()
+        from . import program
+        program.reset_sync()
         raise KernelError(f"a kernel reported a fault (status {code}: bits 0-2 a barrier wait ran out in the "
                           "tensor-core product, bit 3 a key/value write and bit 4 a key read had no page behind "
-                          "it); the step's output is not valid")
+                          "it, bits 5-6 a wait ran out in the bulk decode attention, bit 7 in the decode "
+                          "program); the step's output is not valid")
 
 
 def tensor_core_gemm_supported(K: int, N: int) -> bool:
@@ -393,6 +424,7 @@ def tensor_core_gemm_supported(K: int, N: int) -> bool:
 def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> None:
     """out = act(a @ w.T + bias) + residual on the tcgen05 tensor cores.
     a: bfloat16 [M, K]; w: bfloat16 [N, K]; out: bfloat16 or float32 [M, N]."""
+    _no_record("a tensor-memory product")
     _cuda(a, w, bias, out, residual)
     M, K = a.shape
     N = w.shape[0]
@@ -479,6 +511,10 @@ def gemm_skinny(a, w, bias, out, *, act=None, residual=None, norm=None, kv=None)
         if kc.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kv_cols != hkv * head_dim \
                 or q_cols + 2 * kv_cols != N or kv.head_dim != head_dim:
             raise KernelError("gemm_skinny: the key/value target does not match the product")
+    if _recorder is not None:
+        kvrec = None if kv is None else (kc, vc, table, tseq, tpos, page_stride, q_cols, kv_cols, head_dim,
+                                         page_size, num_pages)
+        return _recorder.gemm(a, x, gamma, beta, eps, w, bias, residual, out, ACT_CODES[act], _dt(out), kvrec)
     lib = load_library("gemm_skinny")
     code = lib.sandy_gemm_skinny(
         _p(a), _p(x), ctypes.c_int(0 if x is None else x.stride(0)), _p(gamma), _p(beta), ctypes.c_float(eps),

@@ -28,6 +28,7 @@ reserved beforehand and the drawn tokens of all steps come back in one copy.
 from __future__ import annotations
 
 import dataclasses
+import os
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -35,7 +36,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pages import FREED, OutOfPages
-from ..csrc import ops
+from ..csrc import ops, program
 from ..models.model import Model
 from ..parts.base import StepContext, Workspace
 
@@ -111,7 +112,8 @@ class Engine:
     """A bound model, its cache and the step function over them."""
 
     def __init__(self, model: Model, *, max_tokens: int, page_size: int = 16, max_requests: int = 64,
-                 max_step_tokens: int = 2048, use_cuda_graphs: bool = True):
+                 max_step_tokens: int = 2048, use_cuda_graphs: bool = True,
+                 use_decode_programs: Optional[bool] = None):
         if model.device is None:
             raise StepError("the model has no weights bound")
         if model.device.type != "cuda":
@@ -132,6 +134,15 @@ class Engine:
         self._burst_tokens = torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, device=self.device)
         self._burst_host = torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, pin_memory=True)
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
+        # Optional: decode steps of up to 16 tokens as ONE resident kernel that interprets the step's
+        # operations (csrc/program.py).  Off unless asked for (argument, or SANDYRT_DECODE_PROGRAM=1):
+        # measured on GPT-2 small it is slower than the chain of kernels under a CUDA graph (8
+        # requests: 0.66 ms against 0.40 ms a step), see decode_program.cu.
+        if use_decode_programs is None:
+            use_decode_programs = os.environ.get("SANDYRT_DECODE_PROGRAM", "0") == "1"
+        self.use_decode_programs = bool(use_decode_programs) and self.dtype == torch.bfloat16 and model.graph_safe
+        self._programs: Dict[Tuple, Optional[Tuple]] = {}
+        self.program_runs = 0
         self._graphs: Dict[Tuple, Tuple] = {}
         self._seen: Dict[Tuple, int] = {}
         self._table_rows: Dict[Tuple[Hashable, int], Tuple[int, np.ndarray]] = {}
@@ -320,9 +331,36 @@ class Engine:
         return _Prepared(ctx, sample_dev, key, burst)
 
     # ---- running it ------------------------------------------------------------------------
-    def _run(self, p: _Prepared) -> torch.Tensor:
+    def _program_for(self, p: _Prepared):
+        """The recorded program of this step's shape, recording it on first sight; None if the
+        step is not a small decode step or the model cannot be recorded.  Never called while a
+        CUDA graph is being captured (recording allocates and copies)."""
         ctx = p.ctx
-        logits = self.model.forward(ctx, status=self._status)
+        if not self.use_decode_programs or p.key is None or ctx.max_q_len != 1 \
+                or ctx.n_tokens > program.limits()["max_rows"]:
+            return None
+        hit = self._programs.get(p.key, False)
+        if hit is not False and (hit is None or hit[2] == self.workspace.version):
+            return hit
+        try:
+            with program.recording(self.device, ops.kernel_status(self.device)) as rec:
+                logits = self.model.forward(ctx, status=self._status)
+            hit = (rec.finish(), logits, self.workspace.version)
+        except program.NotRecordable:
+            hit = None
+        while len(self._programs) >= MAX_GRAPHS:
+            del self._programs[next(iter(self._programs))]
+        self._programs[p.key] = hit
+        return hit
+
+    def _run(self, p: _Prepared, prog=None) -> torch.Tensor:
+        ctx = p.ctx
+        if prog is not None:
+            prog[0].run()
+            logits = prog[1]
+            self.program_runs += 1
+        else:
+            logits = self.model.forward(ctx, status=self._status)
         R = ctx.logit_rows.numel()
         if p.sample is not None and R:
             f = p.sample.view(torch.float32)
@@ -339,6 +377,7 @@ class Engine:
     def _execute(self, p: _Prepared, times: int = 1) -> torch.Tensor:
         """Run the prepared step `times` times (more than once only for a burst, whose sampler
         moves the step's inputs on), through a recorded graph where there is one."""
+        prog = self._program_for(p)
         before = ops.LAUNCHES
         key = p.key
         if key is not None and self.use_cuda_graphs:
@@ -360,7 +399,7 @@ class Engine:
                 torch.cuda.current_stream().synchronize()
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
-                    logits = self._run(p)
+                    logits = self._run(p, prog)
                 n_launch = ops.LAUNCHES - before
                 while len(self._graphs) >= MAX_GRAPHS:          # the oldest recording makes room
                     del self._graphs[next(iter(self._graphs))]
@@ -372,7 +411,7 @@ class Engine:
             self._seen[key] = 1
         logits = None
         for _ in range(times):
-            logits = self._run(p)
+            logits = self._run(p, prog)
         self.last_launches = (ops.LAUNCHES - before) // times
         return logits
 
