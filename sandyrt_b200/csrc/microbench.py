@@ -1,0 +1,86 @@
+"""Kernel micro-benchmarks: one kernel alone, inside a CUDA graph, on inputs larger than L2.
+
+    python -m sandyrt_b200.csrc.microbench decode-attention [--heads 12] [--head-dim 64] [--page-size 16]
+
+decode-attention: the register kernel and the bulk-copy kernel of single-token attention on
+several (tokens, context) shapes.  Each timing replays a graph of one launch per distinct cache
+(enough caches to exceed L2), so neither the host's launch cost nor a warm L2 is in the number;
+bytes are the keys and values a launch must read.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+from . import ops
+
+
+def _time_graph(fn, layers: int, reps: int = 3) -> float:
+    """Microseconds per call of fn(l), l = 0..layers-1, replayed from a CUDA graph."""
+    for l in range(layers):
+        fn(l)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        fn(0)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for l in range(layers):
+                fn(l)
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * layers)
+
+
+def decode_attention(a) -> int:
+    dev = torch.device("cuda:0")
+    H, D, PS = a.heads, a.head_dim, a.page_size
+    print("tokens context  kernel    splits       us     GB/s")
+    for T, ctx in ((64, 384), (64, 1024), (256, 384), (8, 384), (8, 1024), (1, 1024)):
+        blocks = -(-ctx // PS)
+        pages = T * blocks
+        bytes_per_launch = T * ctx * H * D * 2 * 2
+        layers = min(48, max(2, int(400e6 // bytes_per_launch) + 1))
+        arena = torch.randn(layers, pages, 2, H, PS, D, device=dev, dtype=torch.bfloat16)
+        table = torch.randperm(pages, device=dev).to(torch.int32).view(T, blocks).contiguous()
+        q = torch.randn(T, H * D, device=dev, dtype=torch.bfloat16)
+        seq = torch.arange(T, device=dev, dtype=torch.int32)
+        pos = torch.full((T,), ctx - 1, device=dev, dtype=torch.int32)
+        out = torch.empty_like(q)
+        splits = min(ops.decode_splits(T, H, blocks * PS), ops.CLUSTER_MAX_SPLITS)
+        for bulk in (False, True):
+            def go(l, bulk=bulk):
+                ops.decode_attention(q, arena[l, :, 0], arena[l, :, 1], table, seq, pos, out, n_heads=H,
+                                     scale=D ** -0.5, num_splits=splits, cluster=True, bulk=bulk)
+            us = _time_graph(go, layers)
+            print(f"{T:6d} {ctx:7d}  {'bulk' if bulk else 'register':8s} {splits:6d} {us:8.2f} {bytes_per_launch / us / 1e3:8.0f}",
+                  flush=True)
+        ops.check_kernel_status(dev)
+        del arena
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="sandyrt_b200.csrc.microbench")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    d = sub.add_parser("decode-attention")
+    d.add_argument("--heads", type=int, default=12)
+    d.add_argument("--head-dim", type=int, default=64)
+    d.add_argument("--page-size", type=int, default=16)
+    d.set_defaults(fn=decode_attention)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
