@@ -68,6 +68,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
@@ -153,6 +157,69 @@ struct EpilogueArgs {
     int act;
     int out_f32;             // 1: float out, 0: bfloat16 out
 };
+
+// Write-back of 32 consecutive columns of one row: bias, activation, residual, rounding, store.
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, int col0, const EpilogueArgs& ep, int M,
+                                            int N) {
+    if (row < M && col0 < N) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            float x = __uint_as_float(r[j]);
+            const int col = col0 + j;
+            if (ep.bias && col < N) x += __bfloat162float(ep.bias[col]);
+            v[j] = apply_act(x, ep.act);
+        }
+        const bool full = col0 + 32 <= N;
+        if (ep.residual) {
+            const float* rr = ep.residual + (size_t)row * ep.ldr + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(rr) & 15) == 0)) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(rr + j);
+                    v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (col0 + j < N) v[j] += rr[j];
+            }
+        }
+        if (ep.out_f32) {
+            float* o = reinterpret_cast<float*>(ep.out) + (size_t)row * ep.ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (col0 + j < N) o[j] = v[j];
+            }
+        } else {
+            bf16* o = reinterpret_cast<bf16*>(ep.out) + (size_t)row * ep.ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 pk;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                    *reinterpret_cast<uint4*>(o + j) = pk;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (col0 + j < N) o[j] = __float2bfloat16_rn(v[j]);
+            }
+        }
+    }
+}
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -256,65 +323,158 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
                 tmem_wait_ld();
-                const int col0 = n0 + c * 32;
-                if (row < M && col0 < N) {
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        float x = __uint_as_float(r[j]);
-                        const int col = col0 + j;
-                        if (ep.bias && col < N) x += __bfloat162float(ep.bias[col]);
-                        v[j] = apply_act(x, ep.act);
+                store_chunk(r, row, n0 + c * 32, ep, M, N);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---- the persistent form -------------------------------------------------------------------------
+// One CTA per SM walks the output tiles (tile = blockIdx.x, + gridDim.x, ...).  What the
+// one-tile-per-CTA kernel above pays per tile -- barrier and tensor-memory set-up, a cold TMA
+// ring, and above all an MMA pipe that idles while the accumulator is written back -- is paid
+// once, or overlapped: tensor memory holds TWO accumulators, so the MMA warp starts the next
+// tile while eight epilogue warps (two per 32-lane quarter of tensor memory, half of the tile's
+// columns each) drain the last one, and the TMA warp runs ahead across tile boundaries.
+//   warp 0      TMA producer            full[s] / empty[s] ring over all k-steps of all tiles
+//   warp 1      MMA issuer              acc_empty[b] -> k-steps -> commit acc_full[b]
+//   warps 2..9  epilogue                acc_full[b] -> tcgen05.ld, write-back -> acc_empty[b]
+// Tiles are numbered m-fastest, so CTAs that run side by side share a W tile in L2.
+constexpr int P_THREADS = 320;
+constexpr int P_EPI_WARPS = 8;
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                          EpilogueArgs ep, int M, int N, int K, int* __restrict__ status) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* stage_base = smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full = empty_bar + STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;            // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_tiles = (K + BK - 1) / BK;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators; a power of two for BN = 64, 128, 256
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], P_EPI_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            uint32_t it = 0;        // k-steps issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                for (int kt = 0; kt < k_tiles; kt++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1)) {
+                        if (status) atomicOr(status, 1);
+                        ok = false;
+                        break;
                     }
-                    const bool full = col0 + 32 <= N;
-                    if (ep.residual) {
-                        const float* rr = ep.residual + (size_t)row * ep.ldr + col0;
-                        if (full && ((reinterpret_cast<uintptr_t>(rr) & 15) == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 t = *reinterpret_cast<const float4*>(rr + j);
-                                v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (col0 + j < N) v[j] += rr[j];
-                        }
-                    }
-                    if (ep.out_f32) {
-                        float* o = reinterpret_cast<float*>(ep.out) + (size_t)row * ep.ldc + col0;
-                        if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (col0 + j < N) o[j] = v[j];
-                        }
-                    } else {
-                        bf16* o = reinterpret_cast<bf16*>(ep.out) + (size_t)row * ep.ldc + col0;
-                        if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 pk;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                                pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                                pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                                pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                                pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                                *reinterpret_cast<uint4*>(o + j) = pk;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (col0 + j < N) o[j] = __float2bfloat16_rn(v[j]);
-                        }
-                    }
+                    uint8_t* sa = stage_base + s * L::STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, kt * BK, m0, &full_bar[s]);
+                    tma_load_2d(sa + L::A_BYTES, &map_w, kt * BK, n0, &full_bar[s]);
                 }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_instr_desc(BN);
+            uint32_t it = 0;
+            bool ok = true;
+            int ti = 0;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ti++) {
+                const int b = ti & 1;
+                // the accumulator must have been drained by the epilogue of two tiles ago
+                if (!mbar_wait(&acc_empty[b], ((ti >> 1) & 1) ^ 1)) {
+                    if (status) atomicOr(status, 2);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(b * BN);
+                for (int kt = 0; kt < k_tiles; kt++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+                        if (status) atomicOr(status, 2);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(stage_base + s * L::STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + L::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++)
+                        umma_bf16(acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                }
+                if (ok) umma_commit(&acc_full[b]);
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..9 ----------------
+        const int quarter = warp & 3;                  // the TMEM lanes this warp may read
+        const int half = (warp - 2) >> 2;              // which half of the tile's columns
+        constexpr int CHUNKS = BN / 32 / 2;            // 32-column chunks per warp
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ti++) {
+            const int b = ti & 1;
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            if (!mbar_wait(&acc_full[b], (ti >> 1) & 1)) {
+                if (lane == 0 && status) atomicOr(status, 4);
+                break;
+            }
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < CHUNKS; c++) {
+                const int cc = half * CHUNKS + c;
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + cc * 32), r);
+                tmem_wait_ld();
+                if (c == CHUNKS - 1) {
+                    // everything this warp needs of the accumulator is in registers: hand it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[b]);
+                }
+                store_chunk(r, row, n0 + cc * 32, ep, M, N);
             }
         }
     }
@@ -407,12 +567,75 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs& ep,
     return sandy_launch_status();
 }
 
+// Which kernel and tile width for a product.  Both kernels are bound by how fast an SM can pull
+// operand tiles out of L2 (measured here: about 70 GB/s per SM, about 9 TB/s over all SMs), not
+// by the tensor pipe, so the estimate is bytes over bandwidth plus what is not overlapped:
+//   one tile per CTA, c CTAs resident per SM:  rounds(tiles / (SMs * c)) x c x tile bytes / rate + one epilogue
+//   persistent:                                rounds(tiles / SMs) x tile bytes / rate + one epilogue
+// The constants come from `python -m sandyrt_b200.csrc.microbench gemm` (2048 rows, GPT-2 small).
+int choose_tile(int M, int N, int K) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n = 148;
+        sms = n > 0 ? n : 148;
+    }
+    const double rate = 70e3, all_rate = 9e6;        // bytes per microsecond: one SM, all SMs
+    const int k_tiles = (K + BK - 1) / BK, m_tiles = (M + BM - 1) / BM;
+    double best = 1e30;
+    int best_tile = -64;
+    const int widths[3] = {64, 128, 256};
+    for (int persistent = 0; persistent < 2; persistent++) {
+        for (int wi = 0; wi < 3; wi++) {
+            const int bn = widths[wi];
+            const double tile_bytes = (double)k_tiles * (BM + bn) * BK * 2;
+            const long long tiles = (long long)m_tiles * ((N + bn - 1) / bn);
+            const int resident = persistent ? 1 : (bn == 256 ? 1 : 2);
+            const long long rounds = (tiles + (long long)sms * resident - 1) / ((long long)sms * resident);
+            const long long busy = tiles < (long long)sms * resident ? tiles : (long long)sms * resident;
+            const double per_sm = (double)rounds * (double)((busy + sms - 1) / sms < resident ? (busy + sms - 1) / sms : resident)
+                                  * tile_bytes / rate;
+            const double all = (double)tiles * tile_bytes / all_rate;
+            const double epilogue = (persistent ? 3.0 : 2.0) + bn / 64.0 * (persistent ? 0.6 : 1.0);
+            const double t = (per_sm > all ? per_sm : all) + epilogue;
+            if (t < best) {
+                best = t;
+                best_tile = persistent ? bn : -bn;
+            }
+        }
+    }
+    return best_tile;
+}
+
+template <int BN, int STAGES>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs& ep, int M, int N, int K,
+                      int* status, cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    static int sms = 0;
+    if (sms == 0) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0, n = 0;
+        e = cudaGetDevice(&dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        sms = n;
+    }
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    gemm_tc_persistent_kernel<BN, STAGES><<<grid, P_THREADS, L::TOTAL, stream>>>(ma, mw, ep, M, N, K, status);
+    return sandy_launch_status();
+}
+
 }  // namespace
 
 // a: bfloat16 [M, K], row stride lda; w: bfloat16 [N, K], row stride ldw; bias: bfloat16 [N] or
 // null; residual: float [M, N] row stride ldr or null; out: [M, N] row stride ldc, bfloat16
 // (out_dtype 1) or float (out_dtype 0).  Strides in elements; lda, ldw multiples of 8; a and w
-// 16-byte aligned.  tile_n: 0 = choose, else 64, 128 or 256.
+// 16-byte aligned.  tile_n: 0 = choose (choose_tile), else 64, 128 or 256 (the persistent kernel),
+// or -64, -128, -256 (one tile per CTA).
 SANDY_API int sandy_gemm_tc(const void* a, const void* w, const void* bias, const float* residual, void* out,
                             int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype,
                             int tile_n, int* status, cudaStream_t stream) {
@@ -421,20 +644,19 @@ SANDY_API int sandy_gemm_tc(const void* a, const void* w, const void* bias, cons
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return SANDY_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return SANDY_ERR_UNSUPPORTED;
     if (out_dtype != SANDY_F32 && out_dtype != SANDY_BF16) return SANDY_ERR_UNSUPPORTED;
-    if (tile_n == 0) {
-        // Fill the 148 SMs: wide tiles when there are plenty, narrow ones for small products.
-        const long long tiles128 = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
-        tile_n = tiles128 >= 2 * 148 ? 128 : 64;
-        if (tiles128 >= 8 * 148) tile_n = 256;
-    }
+    if (tile_n == 0) tile_n = choose_tile(M, N, K);
+    const int box_n = tile_n < 0 ? -tile_n : tile_n;
     CUtensorMap ma, mw;
     if (!get_map(a, M, K, lda, BM, &ma)) return SANDY_ERR_UNSUPPORTED;
-    if (!get_map(w, N, K, ldw, tile_n, &mw)) return SANDY_ERR_UNSUPPORTED;
+    if (!get_map(w, N, K, ldw, box_n, &mw)) return SANDY_ERR_UNSUPPORTED;
     EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0};
     switch (tile_n) {
-        case 64: return launch<64, 4>(ma, mw, ep, M, N, K, status, stream);
-        case 128: return launch<128, 3>(ma, mw, ep, M, N, K, status, stream);
-        case 256: return launch<256, 4>(ma, mw, ep, M, N, K, status, stream);
+        case -64: return launch<64, 4>(ma, mw, ep, M, N, K, status, stream);
+        case -128: return launch<128, 3>(ma, mw, ep, M, N, K, status, stream);
+        case -256: return launch<256, 4>(ma, mw, ep, M, N, K, status, stream);
+        case 64: return launch_persistent<64, 8>(ma, mw, ep, M, N, K, status, stream);
+        case 128: return launch_persistent<128, 6>(ma, mw, ep, M, N, K, status, stream);
+        case 256: return launch_persistent<256, 4>(ma, mw, ep, M, N, K, status, stream);
         default: return SANDY_ERR_UNSUPPORTED;
     }
 }

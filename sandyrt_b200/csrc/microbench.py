@@ -1,6 +1,7 @@
 """Kernel micro-benchmarks: one kernel alone, inside a CUDA graph, on inputs larger than L2.
 
     python -m sandyrt_b200.csrc.microbench decode-attention [--heads 12] [--head-dim 64] [--page-size 16]
+    python -m sandyrt_b200.csrc.microbench gemm [--rows 2048] [--width 768] [--inner 3072]
 
 decode-attention: the register kernel and the bulk-copy kernel of single-token attention on
 several (tokens, context) shapes.  Each timing replays a graph of one launch per distinct cache
@@ -70,6 +71,32 @@ def decode_attention(a) -> int:
     return 0
 
 
+def gemm(a) -> int:
+    """The tcgen05 product at the shapes of a prompt step, every tile choice; activations and
+    weights of `layers` distinct layers so that the operands do not sit in L2 between launches."""
+    dev = torch.device("cuda:0")
+    M = a.rows
+    shapes = [("q/k/v", 3 * a.width, a.width, None, False), ("out-projection", a.width, a.width, None, True),
+              ("up-projection", a.inner, a.width, "gelu_new", False), ("down-projection", a.width, a.inner, None, True)]
+    print(f"rows {M}; us per launch (TFLOP/s) by tile width; negative widths: one tile per CTA")
+    layers = 12
+    for name, N, K, act, res in shapes:
+        xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(layers)]
+        ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05 for _ in range(layers)]
+        bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(M, N, device=dev, dtype=torch.float32 if res else torch.bfloat16)
+        resid = torch.randn(M, N, device=dev, dtype=torch.float32) if res else None
+        line = f"{name:16s} {M}x{N}x{K}:"
+        for tile in (-64, -128, -256, 64, 128, 256):
+            def go(l, tile=tile):
+                ops.gemm_tc(xs[l], ws[l], bias, out, act=act, residual=resid, tile_n=tile)
+            us = _time_graph(go, layers)
+            line += f"  {tile:5d}: {us:6.1f} ({2.0 * M * N * K / us / 1e6:5.0f})"
+        print(line, flush=True)
+        ops.check_kernel_status(dev)
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="sandyrt_b200.csrc.microbench")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -78,6 +105,11 @@ def main(argv=None) -> int:
     d.add_argument("--head-dim", type=int, default=64)
     d.add_argument("--page-size", type=int, default=16)
     d.set_defaults(fn=decode_attention)
+    g = sub.add_parser("gemm")
+    g.add_argument("--rows", type=int, default=2048)
+    g.add_argument("--width", type=int, default=768)
+    g.add_argument("--inner", type=int, default=3072)
+    g.set_defaults(fn=gemm)
     a = ap.parse_args(argv)
     return a.fn(a)
 

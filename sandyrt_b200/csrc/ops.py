@@ -443,12 +443,52 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> Non
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N):
         raise KernelError("gemm_tc: bias must be bfloat16 [N]")
     lib = load_library("gemm_tc")
-    code = lib.sandy_gemm_tc(_p(a), _p(w), _p(bias), _p(residual), _p(out), ctypes.c_int(M), ctypes.c_int(N),
-                             ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
-                             ctypes.c_int(0 if residual is None else residual.stride(0)),
-                             ctypes.c_int(out.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(out)),
-                             ctypes.c_int(tile_n), _p(kernel_status(a.device)), _stream())
-    _check(code, f"gemm_tc(M={M},N={N},K={K})")
+
+    def launch(tile, dst, res):
+        code = lib.sandy_gemm_tc(_p(a), _p(w), _p(bias), _p(res), _p(dst), ctypes.c_int(M), ctypes.c_int(N),
+                                 ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
+                                 ctypes.c_int(0 if res is None else res.stride(0)),
+                                 ctypes.c_int(dst.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(dst)),
+                                 ctypes.c_int(tile), _p(kernel_status(a.device)), _stream())
+        _check(code, f"gemm_tc(M={M},N={N},K={K},tile={tile})")
+
+    if tile_n == 0 and M >= GEMM_TUNE_MIN_ROWS:
+        tile_n = _tuned_tile(launch, a, out, residual, M, N, K, act)
+    launch(tile_n, out, residual)
+
+
+# Which of the six tcgen05 variants (three tile widths, one tile per CTA or persistent) is fastest
+# depends on how the tiles of a product fall on the 148 SMs, and a model of it was off by 20 % on
+# half the shapes tried.  So the first product of a shape (rows in steps of 128) with at least
+# this many rows times each variant on a scratch output and remembers the winner.  All variants
+# add the k-steps of an output element in the same order, so the choice never changes a result.
+# Not done while a CUDA graph is being captured (the kernel's own default stands then).
+GEMM_TUNE_MIN_ROWS = 256
+_gemm_tiles: dict = {}
+
+
+def _tuned_tile(launch, a, out, residual, M: int, N: int, K: int, act) -> int:
+    key = (-(-M // 128), N, K, ACT_CODES[act], residual is not None, out.dtype, a.device.index)
+    hit = _gemm_tiles.get(key)
+    if hit is not None:
+        return hit
+    if torch.cuda.is_current_stream_capturing():
+        return 0
+    scratch = torch.empty_like(out)
+    best, best_us = 0, float("inf")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for tile in (-64, -128, -256, 64, 128, 256):
+        launch(tile, scratch, residual)
+        e0.record()
+        for _ in range(3):
+            launch(tile, scratch, residual)
+        e1.record()
+        e1.synchronize()
+        us = e0.elapsed_time(e1)
+        if us < best_us:
+            best, best_us = tile, us
+    _gemm_tiles[key] = best
+    return best
 
 
 SKINNY_NORM_MAX_ROWS = 16
