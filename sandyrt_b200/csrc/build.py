@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "norm": [],
     "gemm_simt": [],
     "gemm_tc": [],
+    "gemm_tc2": [],
     "gemm_skinny": [],
     "attention": [],
     "attention_decode": [],

@@ -78,7 +78,7 @@ def gemm(a) -> int:
     M = a.rows
     shapes = [("q/k/v", 3 * a.width, a.width, None, False), ("out-projection", a.width, a.width, None, True),
               ("up-projection", a.inner, a.width, "gelu_new", False), ("down-projection", a.width, a.inner, None, True)]
-    print(f"rows {M}; us per launch (TFLOP/s) by tile width; negative widths: one tile per CTA")
+    print(f"rows {M}; us per launch (TFLOP/s) by tile width; negative: one tile per CTA; 2000+: two CTAs a tile")
     layers = 12
     for name, N, K, act, res in shapes:
         xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(layers)]
@@ -87,7 +87,7 @@ def gemm(a) -> int:
         out = torch.empty(M, N, device=dev, dtype=torch.float32 if res else torch.bfloat16)
         resid = torch.randn(M, N, device=dev, dtype=torch.float32) if res else None
         line = f"{name:16s} {M}x{N}x{K}:"
-        for tile in (-64, -128, -256, 64, 128, 256):
+        for tile in ops.GEMM_VARIANTS:
             def go(l, tile=tile):
                 ops.gemm_tc(xs[l], ws[l], bias, out, act=act, residual=resid, tile_n=tile)
             us = _time_graph(go, layers)

@@ -445,11 +445,14 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> Non
     lib = load_library("gemm_tc")
 
     def launch(tile, dst, res):
-        code = lib.sandy_gemm_tc(_p(a), _p(w), _p(bias), _p(res), _p(dst), ctypes.c_int(M), ctypes.c_int(N),
-                                 ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
-                                 ctypes.c_int(0 if res is None else res.stride(0)),
-                                 ctypes.c_int(dst.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(dst)),
-                                 ctypes.c_int(tile), _p(kernel_status(a.device)), _stream())
+        fn = lib.sandy_gemm_tc
+        if tile >= PAIR_TILE:        # two CTAs on one 256-row tile
+            fn, tile = load_library("gemm_tc2").sandy_gemm_tc2, tile - PAIR_TILE
+        code = fn(_p(a), _p(w), _p(bias), _p(res), _p(dst), ctypes.c_int(M), ctypes.c_int(N),
+                  ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
+                  ctypes.c_int(0 if res is None else res.stride(0)),
+                  ctypes.c_int(dst.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(dst)),
+                  ctypes.c_int(tile), _p(kernel_status(a.device)), _stream())
         _check(code, f"gemm_tc(M={M},N={N},K={K},tile={tile})")
 
     if tile_n == 0 and M >= GEMM_TUNE_MIN_ROWS:
@@ -457,13 +460,16 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> Non
     launch(tile_n, out, residual)
 
 
-# Which of the six tcgen05 variants (three tile widths, one tile per CTA or persistent) is fastest
+# Which of the tcgen05 variants (three tile widths, one tile per CTA or persistent; two CTAs on a
+# 256-row tile, two widths) is fastest
 # depends on how the tiles of a product fall on the 148 SMs, and a model of it was off by 20 % on
 # half the shapes tried.  So the first product of a shape (rows in steps of 128) with at least
 # this many rows times each variant on a scratch output and remembers the winner.  All variants
 # add the k-steps of an output element in the same order, so the choice never changes a result.
 # Not done while a CUDA graph is being captured (the kernel's own default stands then).
 GEMM_TUNE_MIN_ROWS = 256
+PAIR_TILE = 2000          # tile_n = PAIR_TILE + 128 or + 256: the two-CTA kernel (gemm_tc2.cu)
+GEMM_VARIANTS = (-64, -128, -256, 64, 128, 256, PAIR_TILE + 128, PAIR_TILE + 256)
 _gemm_tiles: dict = {}
 
 
@@ -477,7 +483,7 @@ def _tuned_tile(launch, a, out, residual, M: int, N: int, K: int, act) -> int:
     scratch = torch.empty_like(out)
     best, best_us = 0, float("inf")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for tile in (-64, -128, -256, 64, 128, 256):
+    for tile in GEMM_VARIANTS:
         launch(tile, scratch, residual)
         e0.record()
         for _ in range(3):

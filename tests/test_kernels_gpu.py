@@ -112,10 +112,11 @@ def test_gemm_simt(dtype, M, N, K, layout):
 
 @pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 2304, 768), (100, 777, 240), (128, 128, 64), (129, 130, 72),
                                    (300, 1000, 96), (2048, 768, 3072), (257, 320, 96), (64, 50257, 64), (517, 96, 320)])
-@pytest.mark.parametrize("tile_n", [0, 64, 128, 256, -64, -128, -256])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256, -64, -128, -256, 2128, 2256])
 def test_gemm_tc(M, N, K, tile_n):
     """The tcgen05 kernels (positive tile widths: the persistent kernel; negative: one tile per
-    CTA) at sizes that are no multiple of their tiles, every epilogue."""
+    CTA; 2000 + width: two CTAs on a 256-row tile) at sizes that are no multiple of their tiles,
+    every epilogue."""
     from sandyrt_b200.csrc import ops
 
     a = _rand((M, K), torch.bfloat16, 1)
