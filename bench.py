@@ -134,9 +134,9 @@ def _start_decoding(llm, batch, prompt_len, max_tokens, warmup, rng, vocab):
 
 def _drop(llm, rids):
     for r in rids:
-        if r in llm.engine.cache.alloc:
-            llm.engine.release(r)
-        llm.scheduler.running = [q for q in llm.scheduler.running if q.rid != r]
+        llm.abort(r)
+    llm.drain()
+    for r in rids:
         llm.forget(r)
 
 
@@ -145,27 +145,35 @@ def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, want_e2e=True)
 
     device: the engine's step (index arrays copied from pinned memory, model, sampler), steps
             issued back to back with no read-back in between, timed with CUDA events;
-    e2e:    the same number of steps through the entry point (LLM.step: scheduler, host token
-            ids in, drawn tokens read back to the host every step), timed on the wall clock.
+    e2e:    the same number of steps through the entry point (LLM.step: scheduler, bursts of
+            decode steps with the drawn tokens of every step read back to the host), timed on
+            the wall clock.
 
-    Returns (device ms/step, e2e ms/step, mean context length, launches per step)."""
+    Returns (device ms/step, (e2e ms/step, host-to-device and device-to-host bytes per step of that
+    loop), mean context length, launches per step)."""
     import torch
 
     from sandyrt_b200.engine.step import SampleRow, StepEntry
 
-    e2e_ms = None
+    e2e_ms, e2e_h2d, e2e_d2h = None, 0.0, 0.0
     if want_e2e:
         rids = _start_decoding(llm, batch, prompt_len, steps + 10 * warmup + 80, warmup, rng, vocab)
         torch.cuda.synchronize()
         first = llm.decode_steps_run
+        h2d0, d2h0 = llm.engine.h2d_bytes_total, llm.engine.d2h_bytes_total
         t0 = time.perf_counter()
         while llm.decode_steps_run - first < steps:     # a call may run a burst of several steps
             llm.step()
+        llm.drain()                                     # a burst queued ahead: its steps count, and so does its time
         torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / (llm.decode_steps_run - first)
+        n_steps = llm.decode_steps_run - first
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / n_steps
+        e2e_h2d = (llm.engine.h2d_bytes_total - h2d0) / n_steps
+        e2e_d2h = (llm.engine.d2h_bytes_total - d2h0) / n_steps
         _drop(llm, rids)
 
     rids = _start_decoding(llm, batch, prompt_len, 100000, warmup, rng, vocab)
+    llm.drain()                                          # the loop below drives the engine itself
     engine = llm.engine
     ctx0 = sum(engine.length(r) for r in rids) / batch
     rows = [SampleRow() for _ in rids]
@@ -183,7 +191,7 @@ def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, want_e2e=True)
     ctx1 = sum(engine.length(r) for r in rids) / batch
     launches = engine.last_launches
     _drop(llm, rids)
-    return dev_ms, e2e_ms, 0.5 * (ctx0 + ctx1), launches
+    return dev_ms, (e2e_ms, e2e_h2d, e2e_d2h), 0.5 * (ctx0 + ctx1), launches
 
 
 def main() -> int:
@@ -222,10 +230,13 @@ def main() -> int:
     clocks.start()
 
     # ---- decode at the headline batch: device-timed step of the engine + sampler ------------
-    # The same loop gives the end-to-end number: every llm.step() packs the step's host token
-    # ids into pinned memory, copies them to the device, runs the model and the sampler and
-    # reads the drawn tokens back to the host before the next step is planned.
-    dev_ms, wall_ms, mean_ctx, launches_per_step = decode_run(llm, args.batch, args.prompt_len, args.steps,
+    # The same loop gives the end-to-end number through the entry point.  While all requests are
+    # decoding, llm.step() runs bursts of up to 8 decode steps: a burst's index arrays, block
+    # tables and sampling options are packed into pinned memory and copied to the device, the
+    # sampler feeds each drawn token to the next step on the device, and every step's drawn
+    # tokens are copied back to pinned memory and handed to the scheduler; the next burst is
+    # queued before the last one's tokens are read.  The byte counts are those copies, per step.
+    dev_ms, (wall_ms, e2e_h2d, e2e_d2h), mean_ctx, launches_per_step = decode_run(llm, args.batch, args.prompt_len, args.steps,
                                                               args.warmup, rng, vocab)
     value = args.batch / (dev_ms / 1e3)
     e2e_value = args.batch / (wall_ms / 1e3)
@@ -275,7 +286,8 @@ def main() -> int:
                    "parallelism": "single-gpu", "weights": "random seed 0",
                    "l2": "inputs larger than L2 (weights %.0f MB)" % (weight_bytes / 1e6)},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": wall_ms,
-                "h2d_bytes_per_step": engine.last_h2d_bytes, "d2h_bytes_per_step": 4 * args.batch},
+                "h2d_bytes_per_step": round(e2e_h2d, 1), "d2h_bytes_per_step": round(e2e_d2h, 1),
+                "steps_per_burst": llm.max_burst, "bursts_queued_ahead": bool(llm.pipeline_bursts)},
         "gpu_launches": launches,
         "prefill": {"value": T / (pf_ms / 1e3), "tokens": T, "ms": pf_ms, "frac": pf_frac,
                     "peak": f"{peaks['bf16_tflops']} TFLOP/s bf16 of {peaks['source']}"},

@@ -28,6 +28,7 @@ from ..models.model import Model, load_model
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import fresh_seed, uniform_for
 from .scheduler import Portion, Request, RequestRefused, RequestState, Scheduler, StepPlan
+from ..cache.pages import OutOfPages
 from .step import MAX_BURST, Engine, SampleRow, StepEntry
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -56,14 +57,17 @@ class LLM:
                  cache_tokens: Optional[int] = None, page_size: int = 16, max_live: int = 64,
                  max_step_tokens: int = 2048, prefill_chunk_tokens: int = 2048,
                  eos_token_ids: Optional[Sequence[int]] = None, max_context_tokens: int = 0,
-                 use_cuda_graphs: bool = True, max_burst: int = 8):
+                 use_cuda_graphs: bool = True, max_burst: int = 8, pipeline_bursts: bool = True):
         """cache_tokens: how many tokens the cache pool holds (default: room for `max_live`
         requests of full length, capped at 1M tokens).  eos_token_ids: stop tokens added to
         every request (default: the config's eos_token_id is NOT added; pass it to stop there).
         max_context_tokens: if > 0, a lower limit on a request's length than the model's.
         max_burst: most decode steps run on the device between two looks of the host (1 = the
         host sees every token as it is drawn; more = fewer round trips, tokens arrive in groups,
-        and up to max_burst - 1 steps of a request that has just hit a stop token are wasted)."""
+        and up to max_burst - 1 steps of a request that has just hit a stop token are wasted).
+        pipeline_bursts: queue the next burst on the device before the tokens of the last one
+        have been read (a request that stops is then noticed one burst later, its extra rows are
+        wasted work; the tokens delivered are the same)."""
         if not torch.cuda.is_available():
             raise RuntimeError("sandyrt_b200 needs a CUDA device; there is no CPU path")
         if isinstance(model, Model):
@@ -84,6 +88,12 @@ class LLM:
         self.eos_token_ids = frozenset(int(t) for t in (eos_token_ids or ()))
         self.max_burst = max(1, min(int(max_burst), MAX_BURST)) if self.engine.use_cuda_graphs else 1
         self.decode_steps_run = 0
+        # A burst queued on the device whose tokens the host has not read yet: (handle, requests).
+        # While one is in flight the next may be queued behind it (see _advance), so the device
+        # does not wait for the host between bursts.
+        self._inflight: Optional[Tuple[object, List[Request]]] = None
+        self.pipeline_bursts = pipeline_bursts
+        self.bursts_queued_ahead = 0
         self._requests: Dict[Hashable, Request] = {}
         self._seeds: Dict[Hashable, int] = {}
         self._next_id = 0
@@ -120,60 +130,102 @@ class LLM:
         and never past a request's token limit, the model's positions or the free pages."""
         if self.max_burst <= 1 or self.scheduler.waiting or not plan.portions:
             return 1
-        n = self.max_burst
         for p in plan.portions:
-            r = p.request
-            if p.count != 1 or not p.samples or not r.output:
+            if p.count != 1 or not p.samples or not p.request.output:
                 return 1
-            n = min(n, r.max_tokens - len(r.output))
+        return self._steps_possible([p.request for p in plan.portions], 0)
+
+    def _steps_possible(self, reqs: Sequence[Request], in_flight: int) -> int:
+        """Steps (at most max_burst, possibly 0) that all of `reqs` can still take when they are
+        already `in_flight` steps ahead of what the host has seen: no request past its token limit
+        or the model's positions, and pages for all of them."""
+        n = self.max_burst
+        for r in reqs:
+            n = min(n, r.max_tokens - len(r.output) - in_flight)
             if self.max_positions is not None:
-                n = min(n, self.max_positions - r.computed)
+                n = min(n, self.max_positions - r.computed - in_flight)
         alloc = self.engine.cache.alloc
         while n > 1:
             need = [0] * len(alloc.pools)
-            for p in plan.portions:
-                for g, k in enumerate(alloc.pages_needed(p.request.rid, p.request.computed + n)):
+            for r in reqs:
+                for g, k in enumerate(alloc.pages_needed(r.rid, r.computed + in_flight + n)):
                     need[g] += k
             if all(k <= alloc.free_pages(g) for g, k in enumerate(need)):
                 break
             n //= 2
-        return max(n, 1)
+        return max(n, 1 if in_flight == 0 else 0)
 
-    def _step_burst(self, plan: StepPlan, n: int) -> List[Tuple[Request, int]]:
-        """n decode steps in one go (Engine.decode_burst), then the scheduler's bookkeeping for
-        each of them in order.  A request that finishes part of the way keeps only the tokens up
-        to its finish; what the device computed for it after that is dropped."""
-        reqs = [p.request for p in plan.portions]
-        entries = [StepEntry(r.rid, [r.tokens[-1]], [0]) for r in reqs]
+    def _queue_burst(self, reqs: List[Request], n: int, in_flight: int):
+        """Queue n decode steps of `reqs` on the device (behind `in_flight` steps already queued)."""
+        entries = [StepEntry(r.rid, [0 if in_flight else r.tokens[-1]], [0]) for r in reqs]
         rows, uniforms = [], np.zeros((n, len(reqs)), dtype=np.float32)
         for i, r in enumerate(reqs):
             sp = r.sampling
             rows.append(SampleRow(0.0 if sp.greedy else sp.temperature, sp.top_k, sp.top_p, 0.0))
             if not sp.greedy:
                 for j in range(n):
-                    uniforms[j, i] = uniform_for(self._seeds[r.rid], len(r.output) + j)
-        tokens = self.engine.decode_burst(entries, rows, uniforms)
-        if (tokens < 0).any():
-            self.engine.check_status()
-            raise ValueError("sampling logits must not contain NaN")         # Sampler.cpp:64-67
+                    uniforms[j, i] = uniform_for(self._seeds[r.rid], len(r.output) + in_flight + j)
+        return self.engine.decode_burst_async(entries, rows, uniforms, in_flight=in_flight)
+
+    def _collect_burst(self, handle, reqs: List[Request]) -> List[Tuple[Request, int]]:
+        """Read a queued burst's tokens and do the scheduler's bookkeeping for each of its steps in
+        order.  A request that finishes part of the way (or was finished or aborted while the
+        burst ran) keeps only the tokens up to its finish; what the device computed for it after
+        that is dropped."""
+        tokens = self.engine.burst_tokens(handle)
+        n = handle.n
         self.decode_steps_run += n
         now = time.perf_counter()
         got: List[Tuple[Request, int]] = []
-        alive = list(range(len(reqs)))
+        alive = [i for i, r in enumerate(reqs) if r.state is RequestState.RUNNING]
+        if any(int(tokens[j, i]) < 0 for j in range(n) for i in alive):
+            self.engine.check_status()
+            raise ValueError("sampling logits must not contain NaN")         # Sampler.cpp:64-67
         for j in range(n):
+            if not alive:
+                break
             sub = StepPlan([Portion(reqs[i], reqs[i].computed, 1, True) for i in alive], [])
             sampled = {reqs[i].rid: int(tokens[j, i]) for i in alive}
             got += [(reqs[i], int(tokens[j, i])) for i in alive]
             for r in self.scheduler.complete(sub, sampled):
                 r.t_finished = now
             alive = [i for i in alive if reqs[i].state is RequestState.RUNNING]
-            if not alive:
-                break
         return got
+
+    def _advance(self) -> List[Tuple[Request, int]]:
+        """A burst is in flight.  If its requests can all go on (nobody is waiting to be admitted,
+        nobody is known to have finished, tokens, positions and pages allow it), queue the next
+        burst behind it BEFORE reading its tokens; then read them.  A request that turns out to
+        have stopped inside the burst just read has wasted rows in the one queued behind it,
+        nothing more: its pages are given back at once, but anything that could reuse them is
+        queued on the same stream behind that burst."""
+        handle, reqs = self._inflight
+        nxt = None
+        if self.pipeline_bursts and not self.scheduler.waiting \
+                and all(r.state is RequestState.RUNNING for r in reqs):
+            n = self._steps_possible(reqs, handle.n)
+            if n >= 1:
+                try:
+                    nxt = self._queue_burst(reqs, n, handle.n)
+                    self.bursts_queued_ahead += 1
+                except OutOfPages:
+                    nxt = None
+        got = self._collect_burst(handle, reqs)
+        self._inflight = (nxt, reqs) if nxt is not None else None
+        return got
+
+    def _step_burst(self, plan: StepPlan, n: int) -> List[Tuple[Request, int]]:
+        """Queue n decode steps (Engine.decode_burst_async) and hand them to _advance, which may
+        queue the following burst before it reads this one's tokens."""
+        reqs = [p.request for p in plan.portions]
+        self._inflight = (self._queue_burst(reqs, n, 0), reqs)
+        return self._advance()
 
     def step(self) -> List[Tuple[Request, int]]:
         """Plan and run one step (or, when every request is decoding, a burst of steps on the
         device).  Returns (request, token) for every token drawn, in order."""
+        if self._inflight is not None:
+            return self._advance()
         plan = self.scheduler.plan()
         if not plan.portions:
             return []
@@ -203,6 +255,7 @@ class LLM:
             if self._token_host.numel() < n:
                 self._token_host = torch.empty(n, dtype=torch.int32, pin_memory=True)
             self._token_host[:n].copy_(tokens, non_blocking=True)
+            self.engine.d2h_bytes_total += 4 * n
             torch.cuda.current_stream().synchronize()
             host = self._token_host[:n].tolist()
             if any(t < 0 for t in host):
@@ -233,6 +286,16 @@ class LLM:
 
     def abort(self, rid: Hashable) -> None:
         self.scheduler.abort(rid, "cancelled")
+
+    def drain(self) -> List[Tuple[Request, int]]:
+        """Read the bursts still queued on the device (and do their bookkeeping) without queueing
+        anything new.  Returns the tokens they drew for requests that were still running."""
+        got: List[Tuple[Request, int]] = []
+        while self._inflight is not None:
+            handle, reqs = self._inflight
+            self._inflight = None
+            got += self._collect_burst(handle, reqs)
+        return got
 
     # ---- the blocking convenience -----------------------------------------------------------
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], *, max_tokens: int = 16,

@@ -93,8 +93,9 @@ class _Staging:
             self.events[i].synchronize()      # the copy that last used this buffer is done
         return i
 
-    def send(self, i: int, n: int) -> None:
-        self.dev[:n].copy_(self.host[i][:n], non_blocking=True)
+    def send(self, i: int, n: int, start: int = 0) -> None:
+        """Copy elements [start, n) of host buffer i to the same place of the device buffer."""
+        self.dev[start:n].copy_(self.host[i][start:n], non_blocking=True)
         if self.events[i] is None:
             self.events[i] = torch.cuda.Event()
         self.events[i].record()
@@ -106,6 +107,15 @@ class _Prepared:
     sample: Optional[torch.Tensor]          # [temperature R | top_k R | top_p R | uniform R] (one step)
     key: Optional[Tuple]                    # graph key, None for steps that are not recorded
     burst: Optional[Tuple[torch.Tensor, torch.Tensor]] = None    # (uniform [n, R], row_step [R]) of a burst
+
+
+@dataclasses.dataclass
+class BurstHandle:
+    """A burst of decode steps queued on the device (Engine.decode_burst_async)."""
+    n: int                       # steps
+    S: int                       # requests
+    host: torch.Tensor           # pinned int32 buffer the tokens are copied to
+    done: torch.cuda.Event       # recorded behind that copy
 
 
 class Engine:
@@ -132,7 +142,10 @@ class Engine:
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._sampled = torch.zeros(max(max_requests, 1), dtype=torch.int32, device=self.device)
         self._burst_tokens = torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, device=self.device)
-        self._burst_host = torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, pin_memory=True)
+        # two pinned buffers: the tokens of one burst are read while the next one runs
+        self._burst_hosts = [torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, pin_memory=True)
+                             for _ in range(2)]
+        self._burst_turn = 0
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
         # Optional: decode steps of up to 16 tokens as ONE resident kernel that interprets the step's
         # operations (csrc/program.py).  Off unless asked for (argument, or SANDYRT_DECODE_PROGRAM=1):
@@ -150,6 +163,8 @@ class Engine:
         self.graph_replays = 0
         self.stale_graphs = 0
         self.last_h2d_bytes = 0
+        self.h2d_bytes_total = 0         # bytes of step arrays copied to the device so far
+        self.d2h_bytes_total = 0         # bytes of drawn tokens copied back so far (bursts; the entry point adds its own)
         self.last_launches = 0
 
     # ---- request lifetime ------------------------------------------------------------
@@ -179,9 +194,13 @@ class Engine:
         return hit[1]
 
     def _prepare(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]],
-                 burst_uniform: Optional[np.ndarray] = None) -> _Prepared:
+                 burst_uniform: Optional[np.ndarray] = None, in_flight: int = 0) -> _Prepared:
         """Check the entries, reserve pages, pack the step's arrays and copy them to the device.
-        burst_uniform: float32 [n_steps, R] for a burst of n_steps decode steps."""
+        burst_uniform: float32 [n_steps, R] for a burst of n_steps decode steps.
+        in_flight: this burst continues one of the same requests that is still running on the
+        device, `in_flight` steps long: every request is that many tokens further than its
+        committed length, and its next token is already where the sampler left it, so the token
+        ids are not sent (everything else is, in stream order behind the running burst)."""
         alloc = self.cache.alloc
         if not entries:
             raise StepError("a step needs at least one token")
@@ -196,7 +215,7 @@ class Engine:
             seen.add(e.rid)
             if e.rid not in alloc:
                 self.admit(e.rid)
-            before = alloc.length(e.rid)
+            before = alloc.length(e.rid) + in_flight
             n = len(e.tokens)
             if limit is not None and before + n + extra > limit:
                 raise StepError(f"request {e.rid!r}: {before + n + extra} tokens exceed the model's {limit} positions")
@@ -223,6 +242,9 @@ class Engine:
         decode_only = max(q_lens) == 1
         if n_burst and (not decode_only or R != S or sampling is None):
             raise StepError("a burst takes single tokens only, each with its logits wanted and sampled")
+        if in_flight and not n_burst:
+            raise StepError("only a burst can continue a burst")
+        generation = self._staging.generation
         page = self.cache.page_size
         max_blocks = max(-(-(b + n + extra) // page) for b, n in zip(kv_before, q_lens))
         max_blocks = max(8, -(-max_blocks // 8) * 8)      # widths in steps of 8: few distinct graphs
@@ -307,8 +329,11 @@ class Engine:
             # last in the buffer: its length changes with the burst, nothing else may move with it
             uv, uni_s = take(n_burst * R)
             uv.view(np.float32)[:] = burst_uniform.reshape(-1)
-        self._staging.send(bi, total)
-        self.last_h2d_bytes = 4 * total
+        if in_flight and self._staging.generation != generation:
+            raise StepError("the step buffer moved under a running burst")
+        self._staging.send(bi, total, start=T if in_flight else 0)
+        self.last_h2d_bytes = 4 * (total - (T if in_flight else 0))
+        self.h2d_bytes_total += self.last_h2d_bytes
 
         def d(sl):
             return dev[sl[0]:sl[0] + sl[1]]
@@ -443,18 +468,39 @@ class Engine:
         of each request's steps as it keeps (`commit`), since a request may have hit a stop token
         part of the way through; what the later steps wrote for it lies beyond its length and is
         never read."""
+        return self.burst_tokens(self.decode_burst_async(entries, sampling, uniforms))
+
+    def decode_burst_async(self, entries: Sequence[StepEntry], sampling: Sequence[SampleRow],
+                           uniforms: np.ndarray, in_flight: int = 0) -> "BurstHandle":
+        """decode_burst without the wait: everything is queued on the stream, including the copy of
+        the drawn tokens to pinned host memory, and a handle comes back for `burst_tokens`.
+        With `in_flight` > 0 the burst continues one of the same requests, in the same order,
+        that was queued before and is `in_flight` steps long (see _prepare): the host can queue
+        the next burst before it has seen the tokens of the last, so its own work between two
+        bursts (scheduling, packing, reading tokens) no longer leaves the device idle.  The
+        entries' token ids are ignored then."""
         n = int(uniforms.shape[0])
         S = len(entries)
         if not (1 <= n <= MAX_BURST):
             raise StepError(f"a burst runs 1 to {MAX_BURST} steps, got {n}")
         if self._burst_tokens.numel() < n * S:
             raise StepError("more requests in a burst than the engine was built for")
-        p = self._prepare(entries, sampling, burst_uniform=np.ascontiguousarray(uniforms, dtype=np.float32))
+        p = self._prepare(entries, sampling, burst_uniform=np.ascontiguousarray(uniforms, dtype=np.float32),
+                          in_flight=in_flight)
         self._execute(p, times=n)
-        self._burst_host[:n * S].copy_(self._burst_tokens[:n * S], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        host = self._burst_hosts[self._burst_turn]
+        self._burst_turn ^= 1
+        host[:n * S].copy_(self._burst_tokens[:n * S], non_blocking=True)
+        self.d2h_bytes_total += 4 * n * S
+        done = torch.cuda.Event()
+        done.record()
         self.steps_run += n
-        return self._burst_host[:n * S].numpy().reshape(n, S).copy()
+        return BurstHandle(n, S, host, done)
+
+    def burst_tokens(self, handle: "BurstHandle") -> np.ndarray:
+        """Wait for a burst queued by decode_burst_async; its tokens, int32 [n, requests]."""
+        handle.done.synchronize()
+        return handle.host[:handle.n * handle.S].numpy().reshape(handle.n, handle.S).copy()
 
     def commit(self, rid: Hashable, new_len: int) -> None:
         """Advance a request's length after a burst (see decode_burst)."""

@@ -182,3 +182,37 @@ def test_bursts_give_the_same_tokens_as_single_steps(model_dirs):
     kw = dict(max_tokens=50)
     assert [r.output_ids for r in tight.generate(prompts, **kw)] == [r.output_ids for r in roomy.generate(prompts, **kw)]
     tight.engine.cache.alloc.check()
+
+
+def test_bursts_queued_ahead_give_the_same_tokens(model_dirs):
+    """The next burst is queued before the last one's tokens are read: same tokens as without,
+    when requests of one batch stop at different times (stop tokens, different limits), when
+    another request arrives in the middle, and two generate calls in a row on one engine."""
+    prompts = _prompts("B", [3, 40, 17, 64], seed=31)
+    for kw in (dict(max_tokens=61), dict(max_tokens=50, temperature=0.9, seed=5)):
+        plain = _llm(model_dirs["B"], pipeline_bursts=False)
+        ahead = _llm(model_dirs["B"], pipeline_bursts=True)
+        a, b = plain.generate(prompts, **kw), ahead.generate(prompts, **kw)
+        assert [r.output_ids for r in a] == [r.output_ids for r in b]
+        assert ahead.bursts_queued_ahead > 0 and plain.bursts_queued_ahead == 0
+        # a stop token that ends one request in the middle of a burst while a later burst is queued
+        stop = a[1].output_ids[20]
+        a2 = plain.generate(prompts, stop_token_ids=[stop], **kw)
+        b2 = ahead.generate(prompts, stop_token_ids=[stop], **kw)
+        assert [r.output_ids for r in a2] == [r.output_ids for r in b2]
+        assert [r.finish_reason for r in a2] == [r.finish_reason for r in b2]
+        assert any(r.finish_reason == "stop" for r in b2)
+        ahead.engine.cache.alloc.check()
+        ahead.engine.check_status()
+    # a request added while bursts are in flight joins after they have drained
+    llm = _llm(model_dirs["B"], pipeline_bursts=True)
+    first = llm.add_request(prompts[1], max_tokens=60)
+    for _ in range(3):
+        llm.step()
+    second = llm.add_request(prompts[2], max_tokens=20)
+    while llm.has_work() or llm._inflight is not None:
+        llm.step()
+    ref = _llm(model_dirs["B"], max_burst=1)
+    assert llm.result(first).output_ids == ref.generate(prompts[1], max_tokens=60)[0].output_ids
+    assert llm.result(second).output_ids == ref.generate(prompts[2], max_tokens=20)[0].output_ids
+    llm.engine.cache.alloc.check()
