@@ -143,14 +143,17 @@ def _drop(llm, rids):
 def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, want_e2e=True):
     """Times `steps` decode steps of `batch` requests after `warmup` untimed ones, twice:
 
-    device: the engine's step (index arrays copied from pinned memory, model, sampler), steps
-            issued back to back with no read-back in between, timed with CUDA events;
+    device: the engine's decode bursts (a burst's index arrays, block tables and sampling options
+            copied from pinned memory; per step the model and the sampler, which feeds the drawn
+            token to the next step on the device), bursts queued back to back with no read-back
+            in between, timed with CUDA events;
     e2e:    the same number of steps through the entry point (LLM.step: scheduler, bursts of
             decode steps with the drawn tokens of every step read back to the host), timed on
             the wall clock.
 
     Returns (device ms/step, (e2e ms/step, host-to-device and device-to-host bytes per step of that
     loop), mean context length, launches per step)."""
+    import numpy as np
     import torch
 
     from sandyrt_b200.engine.step import SampleRow, StepEntry
@@ -177,17 +180,36 @@ def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, want_e2e=True)
     engine = llm.engine
     ctx0 = sum(engine.length(r) for r in rids) / batch
     rows = [SampleRow() for _ in rids]
-    tokens = rng.integers(0, vocab, size=(steps + 2, batch))
-    for i in range(2):                                   # the direct loop's own shape: warm it
-        engine.step([StepEntry(r, [int(tokens[i, k])], [0]) for k, r in enumerate(rids)], sampling=rows)
+    burst = llm.max_burst
+    first = [int(t) for t in rng.integers(0, vocab, size=batch)]
+
+    def queue(n, in_flight):
+        """n more decode steps of all requests, queued behind the in_flight steps already queued."""
+        entries = [StepEntry(r, [0 if in_flight else first[k]], [0]) for k, r in enumerate(rids)]
+        return engine.decode_burst_async(entries, rows, np.zeros((n, batch), dtype=np.float32), in_flight=in_flight)
+
+    # untimed (the entry point's warm-up above has already made the engine record this burst shape)
+    in_flight = 0
+    for _ in range(2):
+        queue(burst, in_flight)
+        in_flight += burst
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
-        engine.step([StepEntry(r, [int(tokens[i + 2, k])], [0]) for k, r in enumerate(rids)], sampling=rows)
+    done = 0
+    while done < steps:
+        n = min(burst, steps - done)
+        last = queue(n, in_flight)
+        in_flight += n
+        done += n
     e1.record()
     torch.cuda.synchronize()
+    if (engine.burst_tokens(last) < 0).any():
+        raise RuntimeError("the sampler reported bad logits")
+    engine.check_status()
     dev_ms = e0.elapsed_time(e1) / steps
+    for r in rids:
+        engine.commit(r, engine.length(r) + in_flight)
     ctx1 = sum(engine.length(r) for r in rids) / batch
     launches = engine.last_launches
     _drop(llm, rids)

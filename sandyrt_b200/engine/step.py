@@ -135,7 +135,7 @@ class Engine:
         self.cache = CacheManager(model.cache_specs(), page_size=page_size, max_tokens=max_tokens,
                                   max_requests=max_requests, device=self.device, dtype=self.dtype)
         self.workspace = Workspace(self.device)
-        blocks_cap = -(-(model.max_positions or max_tokens) // page_size) + 8
+        blocks_cap = -(-(-(-(model.max_positions or max_tokens) // page_size) + 8) // 32) * 32
         cap = 4 * max_step_tokens + 3 * max_requests + 1 + (5 + MAX_BURST) * max_requests \
             + len(self.cache.layout.groups) * max_requests * blocks_cap
         self._staging = _Staging(self.device, 1 << (cap - 1).bit_length())
@@ -146,6 +146,7 @@ class Engine:
         self._burst_hosts = [torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, pin_memory=True)
                              for _ in range(2)]
         self._burst_turn = 0
+        self._burst_flip = 0
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
         # Optional: decode steps of up to 16 tokens as ONE resident kernel that interprets the step's
         # operations (csrc/program.py).  Off unless asked for (argument, or SANDYRT_DECODE_PROGRAM=1):
@@ -247,7 +248,9 @@ class Engine:
         generation = self._staging.generation
         page = self.cache.page_size
         max_blocks = max(-(-(b + n + extra) // page) for b, n in zip(kv_before, q_lens))
-        max_blocks = max(8, -(-max_blocks // 8) * 8)      # widths in steps of 8: few distinct graphs
+        # widths in steps of 8 pages (32 for bursts, whose recordings are dearer): few distinct graphs
+        grain = 32 if n_burst else 8
+        max_blocks = max(8, -(-max_blocks // grain) * grain)
         n_sample = (4 * R if sampling is not None else 0) + (R + n_burst * R if n_burst else 0)
         total = 3 * T + S + (S + 1) + S + R + n_sample + len(groups) * S * max_blocks
         bi = self._staging.acquire(total)
@@ -351,7 +354,12 @@ class Engine:
         # Everything a launch's shape depends on.  The portions' own lengths and starts are device
         # data (q_start, kv_before, positions), so steps that agree on these counts share a graph:
         # decode steps always do, prompt steps do when the token budget is filled the same way.
-        key = (T, S, R, max(q_lens), max_blocks, sampling is not None, n_burst > 0, self._staging.generation)
+        # A burst is recorded whole (all its steps in one graph), in two copies used in turn: a
+        # graph that is launched again while it still runs makes the host wait for it.
+        if n_burst:
+            self._burst_flip ^= 1
+        key = (T, S, R, max(q_lens), max_blocks, sampling is not None, n_burst,
+               self._burst_flip if n_burst else 0, self._staging.generation)
         burst = (d(uni_s).view(torch.float32), d(step_s)) if n_burst else None
         return _Prepared(ctx, sample_dev, key, burst)
 
@@ -399,41 +407,76 @@ class Engine:
                            top_p=f[2 * R:3 * R], uniform=f[3 * R:4 * R], status=self._status)
         return logits
 
+    def _graph_for(self, key: Tuple, record_at: int):
+        """The valid recorded graph of `key`, or None; counts how often the key came by and says
+        whether this is the time to record it."""
+        hit = self._graphs.get(key)
+        if hit is not None and hit[3] != self.workspace.version:
+            # a workspace buffer has moved since this graph was recorded: its pointers are stale
+            del self._graphs[key]
+            self._seen.pop(key, None)
+            hit = None
+            self.stale_graphs += 1
+        if hit is not None:
+            return hit, False
+        seen = self._seen.get(key, 0)
+        self._seen[key] = seen + 1
+        return None, seen >= record_at
+
+    def _record(self, key: Tuple, p: _Prepared, prog, times: int):
+        before = ops.LAUNCHES
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(times):
+                logits = self._run(p, prog)
+        n_launch = (ops.LAUNCHES - before) // times
+        while len(self._graphs) >= MAX_GRAPHS:          # the oldest recording makes room
+            del self._graphs[next(iter(self._graphs))]
+            self._seen.clear()
+        hit = (graph, logits, n_launch, self.workspace.version)
+        self._graphs[key] = hit
+        return hit
+
     def _execute(self, p: _Prepared, times: int = 1) -> torch.Tensor:
         """Run the prepared step `times` times (more than once only for a burst, whose sampler
-        moves the step's inputs on), through a recorded graph where there is one."""
+        moves the step's inputs on), through recorded graphs where there are any.
+
+        Two kinds of recordings.  One step: recorded the second time its shape comes by, replayed
+        `times` times for a burst.  A whole burst (all its steps in one graph, one launch): recorded
+        once the same burst shape has come by three times, so that only workloads that stay in one
+        shape pay for it; kept in two copies used in turn (the key carries the turn), because a
+        graph launched again while it still runs makes the host wait for it, and the host has the
+        next burst to prepare."""
         prog = self._program_for(p)
         before = ops.LAUNCHES
         key = p.key
-        if key is not None and self.use_cuda_graphs:
-            hit = self._graphs.get(key)
-            if hit is not None and hit[3] != self.workspace.version:
-                # a workspace buffer has moved since this graph was recorded: its pointers are stale
-                del self._graphs[key]
-                self._seen.pop(key, None)
-                hit = None
-                self.stale_graphs += 1
+        if key is None or not self.use_cuda_graphs:
+            logits = None
+            for _ in range(times):
+                logits = self._run(p, prog)
+            self.last_launches = (ops.LAUNCHES - before) // times
+            return logits
+        step_key = key
+        if p.burst is not None:
+            step_key = key[:6] + (1, 0) + key[8:]           # any burst length, either turn
+            hit, record = self._graph_for(key, record_at=2)
+            if hit is None and record:
+                hit = self._record(key, p, prog, times)
             if hit is not None:
-                for _ in range(times):
-                    hit[0].replay()
+                hit[0].replay()
                 self.graph_replays += times
                 self.last_launches = hit[2]
                 return hit[1]
-            if self._seen.get(key, 0) >= 1:
-                # the second time a shape comes by it is recorded; the record is then run
-                torch.cuda.current_stream().synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    logits = self._run(p, prog)
-                n_launch = ops.LAUNCHES - before
-                while len(self._graphs) >= MAX_GRAPHS:          # the oldest recording makes room
-                    del self._graphs[next(iter(self._graphs))]
-                self._graphs[key] = (graph, logits, n_launch, self.workspace.version)
-                for _ in range(times):
-                    graph.replay()
-                self.last_launches = n_launch
-                return logits
-            self._seen[key] = 1
+        hit, record = self._graph_for(step_key, record_at=1)
+        if hit is None and record:
+            hit = self._record(step_key, p, prog, 1)
+        if hit is not None:
+            for _ in range(times):
+                hit[0].replay()
+            self.graph_replays += times
+            self.last_launches = hit[2]
+            return hit[1]
         logits = None
         for _ in range(times):
             logits = self._run(p, prog)
