@@ -1,7 +1,7 @@
 """Kernel micro-benchmarks: one kernel alone, inside a CUDA graph, on inputs larger than L2.
 
     python -m sandyrt_b200.csrc.microbench decode-attention [--heads 12] [--head-dim 64] [--page-size 16]
-    python -m sandyrt_b200.csrc.microbench gemm [--rows 2048] [--width 768] [--inner 3072]
+    python -m sandyrt_b200.csrc.microbench gemm [--rows 2048] [--width 768] [--inner 3072] [--k-sweep]
 
 decode-attention: the register kernel and the bulk-copy kernel of single-token attention on
 several (tokens, context) shapes.  Each timing replays a graph of one launch per distinct cache
@@ -94,6 +94,22 @@ def gemm(a) -> int:
             line += f"  {tile:5d}: {us:6.1f} ({2.0 * M * N * K / us / 1e6:5.0f})"
         print(line, flush=True)
         ops.check_kernel_status(dev)
+    if a.k_sweep:
+        # the q/k/v output size at several K, no bias: what does not move with K is launch,
+        # set-up and write-back; the slope is the main loop's rate
+        N = 3 * a.width
+        print(f"K sweep at {M}x{N}, no bias, bfloat16 out: us (TFLOP/s)")
+        for K in (64, 256, 768, 1536, 3072):
+            xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(layers)]
+            ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05 for _ in range(layers)]
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            line = f"K {K:5d}:"
+            for tile in (128, ops.PAIR_TILE + 256):
+                def go(l, tile=tile):
+                    ops.gemm_tc(xs[l], ws[l], None, out, tile_n=tile)
+                us = _time_graph(go, layers)
+                line += f"  {tile:5d}: {us:6.1f} ({2.0 * M * N * K / us / 1e6:5.0f})"
+            print(line, flush=True)
     return 0
 
 
@@ -109,6 +125,7 @@ def main(argv=None) -> int:
     g.add_argument("--rows", type=int, default=2048)
     g.add_argument("--width", type=int, default=768)
     g.add_argument("--inner", type=int, default=3072)
+    g.add_argument("--k-sweep", action="store_true", help="also time the q/k/v output size at several K")
     g.set_defaults(fn=gemm)
     a = ap.parse_args(argv)
     return a.fn(a)
