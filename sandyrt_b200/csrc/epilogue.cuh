@@ -22,6 +22,25 @@ __device__ __forceinline__ float gelu_erf(float u) {
     return 0.5f * u * (1.0f + erff(u * 0.70710678118654752440f));
 }
 
+// gelu_new with tanh(y) = 1 - 2 / (exp(2y) + 1) on the fast exponential and division: a third
+// of tanhf's instructions, absolute error below 1e-6 (exp(2y) overflows to inf for large y,
+// giving exactly 1; underflows to 0 for very negative y, giving exactly -1).  For write-backs
+// that round to bfloat16 or sit in a tensor-core kernel's critical path; the 32-bit path keeps
+// tanhf.
+__device__ __forceinline__ float gelu_tanh_fast(float u) {
+    const float x2 = u * u;
+    const float inner = u + 0.044715f * (x2 * u);
+    const float e = __expf(1.5957691216057308f * inner);        // exp(2 * 0.79788456 * inner)
+    const float t = 1.0f - __fdividef(2.0f, e + 1.0f);
+    return (0.5f * u) * (1.0f + t);
+}
+
+__device__ __forceinline__ float apply_act_fast(float v, int act) {
+    if (act == SANDY_ACT_GELU_TANH) return gelu_tanh_fast(v);
+    if (act == SANDY_ACT_GELU_ERF) return gelu_erf(v);
+    return v;
+}
+
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == SANDY_ACT_GELU_TANH) return gelu_tanh(v);
     if (act == SANDY_ACT_GELU_ERF) return gelu_erf(v);

@@ -134,10 +134,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (ready) {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
+                float4 res[8];
+                const bool have_res = load_residual(res, row, n0 + c * 32, ep, M, N);
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
                 tmem_wait_ld();
-                store_chunk(r, row, n0 + c * 32, ep, M, N);
+                store_chunk(r, row, n0 + c * 32, ep, M, N, res, have_res);
             }
         }
     }
@@ -287,6 +289,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll 1
             for (int c = 0; c < CHUNKS; c++) {
                 const int cc = half * CHUNKS + c;
+                float4 res[8];
+                const bool have_res = load_residual(res, row, n0 + cc * 32, ep, M, N);
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + cc * 32), r);
                 tmem_wait_ld();
@@ -296,7 +300,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[b]);
                 }
-                store_chunk(r, row, n0 + cc * 32, ep, M, N);
+                store_chunk(r, row, n0 + cc * 32, ep, M, N, res, have_res);
             }
         }
     }

@@ -215,6 +215,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll 1
             for (int c = 0; c < CHUNKS; c++) {
                 const int cc = half * CHUNKS + c;
+                float4 res[8];
+                const bool have_res = load_residual(res, row, n0 + cc * 32, ep, M, N);
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + cc * 32), r);
                 tmem_wait_ld();
@@ -224,7 +226,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(in_cta(smem_u32(&acc_empty[b]), 0));
                 }
-                store_chunk(r, row, n0 + cc * 32, ep, M, N);
+                store_chunk(r, row, n0 + cc * 32, ep, M, N, res, have_res);
             }
         }
     }

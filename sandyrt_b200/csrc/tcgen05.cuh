@@ -136,20 +136,38 @@ struct EpilogueArgs {
     int out_f32;             // 1: float out, 0: bfloat16 out
 };
 
+// The residual values of 32 consecutive columns of one row, asked for before the accumulator is
+// read so that the trip to memory overlaps the tensor-memory load.  False (nothing loaded) if
+// there is no residual or it cannot be fetched as eight aligned float4; store_chunk then reads
+// what it needs itself.
+__device__ __forceinline__ bool load_residual(float4 (&res)[8], int row, int col0, const EpilogueArgs& ep, int M, int N) {
+    if (!ep.residual || row >= M || col0 + 32 > N) return false;
+    const float* rr = ep.residual + (size_t)row * ep.ldr + col0;
+    if (reinterpret_cast<uintptr_t>(rr) & 15) return false;
+#pragma unroll
+    for (int j = 0; j < 8; j++) res[j] = *reinterpret_cast<const float4*>(rr + 4 * j);
+    return true;
+}
+
 // Write-back of 32 consecutive columns of one row: bias, activation, residual, rounding, store.
 __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, int col0, const EpilogueArgs& ep, int M,
-                                            int N) {
-    if (row < M && col0 < N) {
-        float v[32];
+                                            int N, const float4 (&res)[8], bool have_res) {
+    // the chunk's 32 bias values: one load per lane, handed round by shuffles (32 scalar loads per
+    // thread were a trip to memory in front of every chunk's arithmetic)
+    const int lane = threadIdx.x & 31;
+    float my_bias = 0.0f;
+    if (ep.bias && col0 + lane < N) my_bias = __bfloat162float(ep.bias[col0 + lane]);
+    float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
-            float x = __uint_as_float(r[j]);
-            const int col = col0 + j;
-            if (ep.bias && col < N) x += __bfloat162float(ep.bias[col]);
-            v[j] = apply_act(x, ep.act);
-        }
+    for (int j = 0; j < 32; j++) v[j] = apply_act_fast(__uint_as_float(r[j]) + __shfl_sync(0xffffffffu, my_bias, j), ep.act);
+    if (row < M && col0 < N) {
         const bool full = col0 + 32 <= N;
-        if (ep.residual) {
+        if (have_res) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                v[4 * j] += res[j].x; v[4 * j + 1] += res[j].y; v[4 * j + 2] += res[j].z; v[4 * j + 3] += res[j].w;
+            }
+        } else if (ep.residual) {
             const float* rr = ep.residual + (size_t)row * ep.ldr + col0;
             if (full && ((reinterpret_cast<uintptr_t>(rr) & 15) == 0)) {
 #pragma unroll
