@@ -144,7 +144,11 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     int has_nan = 0;
-    for (int i = begin; i < end; i++) {
+    // This pass reads the row strided (thread t takes ids t, t + THREADS, ...: whole cache lines per
+    // warp; with each thread on its own contiguous range it cost 13 us for 8 rows of 50257).  A
+    // thread meets its ids in ascending order, so it keeps the first of equal values, and the
+    // merges below prefer the lower id: the result is the first maximum whatever the layout.
+    for (int i = tid; i < vocab; i += THREADS) {
         const float v = row[i];
         if (v != v) has_nan = 1;
         if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
@@ -187,13 +191,13 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
         while (lo < hi) {
             const unsigned mid = lo + (unsigned)(((unsigned long long)hi - lo + 1ull) >> 1);
             int c = 0;
-            for (int i = begin; i < end; i++) c += order_key(row[i]) >= mid;
+            for (int i = tid; i < vocab; i += THREADS) c += order_key(row[i]) >= mid;    // a count: any order
             c = block_sum_int(c, iscratch);
             if (c >= k) lo = mid; else hi = mid - 1u;
         }
         cut_key = lo;
         int above = 0;
-        for (int i = begin; i < end; i++) above += order_key(row[i]) > cut_key;
+        for (int i = tid; i < vocab; i += THREADS) above += order_key(row[i]) > cut_key;
         above = block_sum_int(above, iscratch);
         ties_kept = k - above;
     }
