@@ -351,6 +351,28 @@ def test_prefill_attention_tensor_cores(H, Hkv, D, page_size, window):
     assert (out.double().cpu() - want).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("H,Hkv,D,page_size,window", [(3, 3, 64, 16, 0), (4, 2, 32, 16, 0), (2, 2, 128, 32, 0),
+                                                     (3, 1, 64, 8, 150)])
+def test_prefill_attention_long_portions(H, Hkv, D, page_size, window):
+    """Portions of 256 tokens and more (many key tiles per query tile): a portion from position 0,
+    one behind a long prefix, an odd number of tiles, short ones beside them, a window."""
+    from sandyrt_b200.csrc import ops
+
+    seqs = [(0, 700), (300, 257), (0, 64), (50, 1), (1000, 320)]
+    case = _paged_case(torch.bfloat16, H, Hkv, D, page_size, seqs, seed=D + H)
+    out = torch.full_like(case["q"], float("nan"))
+    scale = 1.0 / math.sqrt(D)
+    lens = [n for _, n in seqs]
+    q_start = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
+    kv_before = torch.tensor([b for b, _ in seqs], dtype=torch.int32, device=DEV)
+    ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
+                          max_q_len=max(lens), scale=scale, window=window)
+    ops.check_kernel_status(DEV)
+    want = _attention_want(case, H, Hkv, D, scale, window)
+    assert not torch.isnan(out).any()
+    assert (out.double().cpu() - want).abs().max().item() < 2e-2
+
+
 def test_prefill_attention_far_key():
     from sandyrt_b200.csrc import ops
 
@@ -367,6 +389,18 @@ def test_prefill_attention_far_key():
         v_far = case["dense_v"][0][far].float()
         got = out[:90].view(90, H, D).float().cpu()
         assert (got - v_far).abs().max().item() < 3e-2, f"far key {far}"
+        # the same with a long portion (five query tiles, up to ten key tiles each)
+        seqs = [(310, 300), (5, 3)]
+        case = _paged_case(torch.bfloat16, H, Hkv, D, 16, seqs, seed=far, spike=(0, far))
+        out = torch.full_like(case["q"], float("nan"))
+        q_start = torch.tensor([0, 300, 303], dtype=torch.int32, device=DEV)
+        kv_before = torch.tensor([310, 5], dtype=torch.int32, device=DEV)
+        ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
+                              max_q_len=300, scale=0.125)
+        if far <= 310:          # visible to every query of the portion
+            v_far = case["dense_v"][0][far].float()
+            got = out[:300].view(300, H, D).float().cpu()
+            assert (got - v_far).abs().max().item() < 3e-2, f"far key {far}, long portion"
 
 
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 32, 33, 64])
