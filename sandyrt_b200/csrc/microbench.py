@@ -92,6 +92,10 @@ def gemm(a) -> int:
                 ops.gemm_tc(xs[l], ws[l], bias, out, act=act, residual=resid, tile_n=tile)
             us = _time_graph(go, layers)
             line += f"  {tile:5d}: {us:6.1f} ({2.0 * M * N * K / us / 1e6:5.0f})"
+        if M <= ops.SKINNY_MAX_ROWS:
+            def go_skinny(l):
+                ops.gemm_skinny(xs[l], ws[l], bias, out, act=act, residual=resid)
+            line += f"  skinny: {_time_graph(go_skinny, layers):6.1f}"
         print(line, flush=True)
         ops.check_kernel_status(dev)
     if a.k_sweep:

@@ -457,6 +457,9 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> Non
 
     if tile_n == 0 and M >= GEMM_TUNE_MIN_ROWS:
         tile_n = _tuned_tile(launch, a, out, residual, M, N, K, act)
+    elif tile_n == 0:
+        tile_n = _gemm_tiles.get((-(-M // 128), N, K, ACT_CODES[act], residual is not None, out.dtype,
+                                  a.device.index), 0)
     launch(tile_n, out, residual)
 
 
@@ -499,6 +502,45 @@ def _tuned_tile(launch, a, out, residual, M: int, N: int, K: int, act) -> int:
 
 SKINNY_NORM_MAX_ROWS = 16
 SKINNY_NORM_MAX_K = 2048
+
+# Between 17 and 64 rows neither kernel always wins (measured at 64 rows on GPT-2 small: the
+# up-projection 5.9 us on tcgen05 against 10.7 us skinny, the out-projection 6.1 against 4.2), so
+# a product of that size with nothing fused into it is timed both ways on first sight, like the
+# tcgen05 variants above.
+_small_choice: dict = {}
+
+
+def small_gemm_prefers_tc(a, w, bias, out, *, act=None, residual=None) -> bool:
+    """Whether a 17..64-row product should go to the tcgen05 kernel instead of the skinny one.
+    Times both once per (rows in steps of 16, N, K, epilogue) on a scratch output; while a CUDA
+    graph is being captured an unknown shape stays with the skinny kernel."""
+    M, K = a.shape
+    N = w.shape[0]
+    key = (-(-M // 16), N, K, ACT_CODES[act], residual is not None, out.dtype, a.device.index)
+    hit = _small_choice.get(key)
+    if hit is not None:
+        return hit
+    if torch.cuda.is_current_stream_capturing() or _recorder is not None:
+        return False
+    scratch = torch.empty_like(out)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for fn in (lambda: gemm_skinny(a, w, bias, scratch, act=act, residual=residual),
+               lambda: gemm_tc(a, w, bias, scratch, act=act, residual=residual, tile_n=64),
+               lambda: gemm_tc(a, w, bias, scratch, act=act, residual=residual, tile_n=-64)):
+        fn()
+        e0.record()
+        for _ in range(3):
+            fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    choice = min(times[1:]) < 0.9 * times[0]          # the skinny kernel keeps ties and near-ties
+    _small_choice[key] = choice
+    if choice:
+        _gemm_tiles[(-(-M // 128), N, K, ACT_CODES[act], residual is not None, out.dtype, a.device.index)] = \
+            64 if times[1] <= times[2] else -64
+    return choice
 
 
 def skinny_norm_fusable(lazy, K: int) -> bool:
