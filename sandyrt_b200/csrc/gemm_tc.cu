@@ -131,6 +131,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!ready && lane == 0 && status) atomicOr(status, 4);
         tc_fence_after();
         const int row = m0 + quarter * 32 + lane;
+        int kv_page, kv_slot;
+        kv_row_target(ep.kv, row, M, kv_page, kv_slot);
         if (ready) {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
@@ -139,7 +141,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
                 tmem_wait_ld();
-                store_chunk(r, row, n0 + c * 32, ep, M, N, res, have_res);
+                store_chunk(r, row, n0 + c * 32, ep, M, N, res, have_res, kv_page, kv_slot, status);
             }
         }
     }
@@ -279,6 +281,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             const int b = ti & 1;
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             const int row = m0 + quarter * 32 + lane;
+            int kv_page, kv_slot;
+            kv_row_target(ep.kv, row, M, kv_page, kv_slot);
             // A warp whose wait ran out keeps walking the tiles but touches nothing any more.
             if (!dead && !mbar_wait(&acc_full[b], (ti >> 1) & 1)) {
                 if (lane == 0 && status) atomicOr(status, 4);
@@ -300,7 +304,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[b]);
                 }
-                store_chunk(r, row, n0 + cc * 32, ep, M, N, res, have_res);
+                store_chunk(r, row, n0 + cc * 32, ep, M, N, res, have_res, kv_page, kv_slot, status);
             }
         }
     }
@@ -399,7 +403,9 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const Epilog
 // or -64, -128, -256 (one tile per CTA).
 SANDY_API int sandy_gemm_tc(const void* a, const void* w, const void* bias, const float* residual, void* out,
                             int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype,
-                            int tile_n, int* status, cudaStream_t stream) {
+                            int tile_n, void* k_cache, void* v_cache, long long page_stride, const int* block_table,
+                            int max_blocks, const int* token_seq, const int* positions, int q_cols, int kv_cols,
+                            int head_dim, int page_size, int num_pages, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return SANDY_OK;
     if (!a || !w || !out || K <= 0) return SANDY_ERR_ARGUMENT;
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return SANDY_ERR_UNSUPPORTED;
@@ -410,7 +416,17 @@ SANDY_API int sandy_gemm_tc(const void* a, const void* w, const void* bias, cons
     CUtensorMap ma, mw;
     if (!get_map(a, M, K, lda, BM, &ma)) return SANDY_ERR_UNSUPPORTED;
     if (!get_map(w, N, K, ldw, box_n, &mw)) return SANDY_ERR_UNSUPPORTED;
-    EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0};
+    KVWrite kv{(bf16*)k_cache, (bf16*)v_cache, page_stride, block_table, token_seq, positions,
+               max_blocks, q_cols, kv_cols, head_dim, page_size, num_pages};
+    if (k_cache) {
+        // the key/value write needs whole heads of a multiple of 16 and the three column ranges
+        if (!v_cache || !block_table || !token_seq || !positions || head_dim <= 0 || head_dim % 16 != 0 ||
+            kv_cols % head_dim != 0 || q_cols % 8 != 0 || q_cols + 2 * kv_cols != N || page_size <= 0 ||
+            (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15) ||
+            page_stride % 8 != 0)
+            return SANDY_ERR_ARGUMENT;
+    }
+    EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0, kv};
     switch (tile_n) {
         case -64: return launch<64, 4>(ma, mw, ep, M, N, K, status, stream);
         case -128: return launch<128, 3>(ma, mw, ep, M, N, K, status, stream);

@@ -205,6 +205,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int b = ti & 1;
             const int m0 = (tile % m_tiles) * PAIR_M + (int)rank * BM, n0 = (tile / m_tiles) * BN;
             const int row = m0 + quarter * 32 + lane;
+            int kv_page, kv_slot;
+            kv_row_target(ep.kv, row, M, kv_page, kv_slot);
             // A warp whose wait ran out keeps walking the tiles but touches nothing any more.
             if (!dead && !mbar_wait(&acc_full[b], (ti >> 1) & 1)) {
                 if (lane == 0 && status) atomicOr(status, 4);
@@ -226,7 +228,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(in_cta(smem_u32(&acc_empty[b]), 0));
                 }
-                store_chunk(r, row, n0 + cc * 32, ep, M, N, res, have_res);
+                store_chunk(r, row, n0 + cc * 32, ep, M, N, res, have_res, kv_page, kv_slot, status);
             }
         }
     }
@@ -280,7 +282,9 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs
 // Arguments as sandy_gemm_tc; tile_n: 128 or 256 (0 = 256).
 SANDY_API int sandy_gemm_tc2(const void* a, const void* w, const void* bias, const float* residual, void* out,
                              int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype,
-                             int tile_n, int* status, cudaStream_t stream) {
+                             int tile_n, void* k_cache, void* v_cache, long long page_stride, const int* block_table,
+                             int max_blocks, const int* token_seq, const int* positions, int q_cols, int kv_cols,
+                             int head_dim, int page_size, int num_pages, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return SANDY_OK;
     if (!a || !w || !out || K <= 0) return SANDY_ERR_ARGUMENT;
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return SANDY_ERR_UNSUPPORTED;
@@ -291,7 +295,17 @@ SANDY_API int sandy_gemm_tc2(const void* a, const void* w, const void* bias, con
     CUtensorMap ma, mw;
     if (!get_map(a, M, K, lda, BM, &ma)) return SANDY_ERR_UNSUPPORTED;
     if (!get_map(w, N, K, ldw, tile_n / 2, &mw)) return SANDY_ERR_UNSUPPORTED;
-    EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0};
+    KVWrite kv{(bf16*)k_cache, (bf16*)v_cache, page_stride, block_table, token_seq, positions,
+               max_blocks, q_cols, kv_cols, head_dim, page_size, num_pages};
+    if (k_cache) {
+        // the key/value write needs whole heads of a multiple of 16 and the three column ranges
+        if (!v_cache || !block_table || !token_seq || !positions || head_dim <= 0 || head_dim % 16 != 0 ||
+            kv_cols % head_dim != 0 || q_cols % 8 != 0 || q_cols + 2 * kv_cols != N || page_size <= 0 ||
+            (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15) ||
+            page_stride % 8 != 0)
+            return SANDY_ERR_ARGUMENT;
+    }
+    EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0, kv};
     if (tile_n == 128) return launch_pair<128, 8>(ma, mw, ep, M, N, K, status, stream);
     return launch_pair<256, 6>(ma, mw, ep, M, N, K, status, stream);
 }

@@ -421,9 +421,10 @@ def tensor_core_gemm_supported(K: int, N: int) -> bool:
     return K % 8 == 0 and K >= 8
 
 
-def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> None:
+def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0, kv=None) -> None:
     """out = act(a @ w.T + bias) + residual on the tcgen05 tensor cores.
-    a: bfloat16 [M, K]; w: bfloat16 [N, K]; out: bfloat16 or float32 [M, N]."""
+    a: bfloat16 [M, K]; w: bfloat16 [N, K]; out: bfloat16 or float32 [M, N].  With `kv` (a
+    KVTarget) the key and value columns of the product also go into the cache pages."""
     _no_record("a tensor-memory product")
     _cuda(a, w, bias, out, residual)
     M, K = a.shape
@@ -442,9 +443,20 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> Non
         raise KernelError("gemm_tc: residual must be float32 [M, N]")
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N):
         raise KernelError("gemm_tc: bias must be bfloat16 [N]")
+    kc = vc = table = tseq = tpos = None
+    page_stride = max_blocks = q_cols = kv_cols = head_dim = page_size = num_pages = 0
+    if kv is not None:
+        hkv, page_size, head_dim, page_stride, num_pages = _cache_args(kv.k_cache, kv.v_cache)
+        kc, vc, table, tseq, tpos = kv.k_cache, kv.v_cache, kv.block_table, kv.token_seq, kv.positions
+        _cuda(kc, vc, table, tseq, tpos)
+        _i32(table, "block_table"); _i32(tseq, "token_seq"); _i32(tpos, "positions")
+        q_cols, kv_cols, max_blocks = kv.q_cols, kv.kv_cols, table.shape[1]
+        if kc.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kv_cols != hkv * head_dim \
+                or q_cols + 2 * kv_cols != N or kv.head_dim != head_dim:
+            raise KernelError("gemm_tc: the key/value target does not match the product")
     lib = load_library("gemm_tc")
 
-    def launch(tile, dst, res):
+    def launch(tile, dst, res, with_kv=True):
         fn = lib.sandy_gemm_tc
         if tile >= PAIR_TILE:        # two CTAs on one 256-row tile
             fn, tile = load_library("gemm_tc2").sandy_gemm_tc2, tile - PAIR_TILE
@@ -452,8 +464,11 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0) -> Non
                   ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
                   ctypes.c_int(0 if res is None else res.stride(0)),
                   ctypes.c_int(dst.stride(0)), ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(dst)),
-                  ctypes.c_int(tile), _p(kernel_status(a.device)), _stream())
-        _check(code, f"gemm_tc(M={M},N={N},K={K},tile={tile})")
+                  ctypes.c_int(tile), _p(kc if with_kv else None), _p(vc), ctypes.c_longlong(page_stride), _p(table),
+                  ctypes.c_int(max_blocks), _p(tseq), _p(tpos), ctypes.c_int(q_cols), ctypes.c_int(kv_cols),
+                  ctypes.c_int(head_dim), ctypes.c_int(page_size), ctypes.c_int(num_pages),
+                  _p(kernel_status(a.device)), _stream())
+        _check(code, f"gemm_tc(M={M},N={N},K={K},tile={tile},kv={kv is not None})")
 
     if tile_n == 0 and M >= GEMM_TUNE_MIN_ROWS:
         tile_n = _tuned_tile(launch, a, out, residual, M, N, K, act)
@@ -486,11 +501,11 @@ def _tuned_tile(launch, a, out, residual, M: int, N: int, K: int, act) -> int:
     scratch = torch.empty_like(out)
     best, best_us = 0, float("inf")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for tile in GEMM_VARIANTS:
-        launch(tile, scratch, residual)
+    for tile in GEMM_VARIANTS:               # timed without the cache write: the scratch runs must not touch pages
+        launch(tile, scratch, residual, False)
         e0.record()
         for _ in range(3):
-            launch(tile, scratch, residual)
+            launch(tile, scratch, residual, False)
         e1.record()
         e1.synchronize()
         us = e0.elapsed_time(e1)

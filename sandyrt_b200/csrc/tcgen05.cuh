@@ -127,6 +127,19 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Where the key and value columns of a fused q/k/v product go (the cache layout of attention.cu):
+// columns [q_cols, q_cols + kv_cols) are keys, the next kv_cols values; row m belongs to
+// position positions[m] of request token_seq[m].  k_cache null: no cache write.
+struct KVWrite {
+    bf16* k_cache;
+    bf16* v_cache;
+    long long page_stride;
+    const int* block_table;
+    const int* token_seq;
+    const int* positions;
+    int max_blocks, q_cols, kv_cols, head_dim, page_size, num_pages;
+};
+
 struct EpilogueArgs {
     const bf16* bias;        // [N] or null
     const float* residual;   // [M, N] row stride ldr, or null
@@ -134,7 +147,19 @@ struct EpilogueArgs {
     int ldr, ldc;
     int act;
     int out_f32;             // 1: float out, 0: bfloat16 out
+    KVWrite kv;
 };
+
+// The page (or -1) and the slot inside it where row `row`'s key and value belong.
+__device__ __forceinline__ void kv_row_target(const KVWrite& kv, int row, int M, int& page, int& slot) {
+    page = -1;
+    slot = 0;
+    if (!kv.k_cache || row >= M) return;
+    const int pos = kv.positions[row];
+    const int b = pos / kv.page_size;
+    slot = pos % kv.page_size;
+    if (pos >= 0 && b < kv.max_blocks) page = kv.block_table[(size_t)kv.token_seq[row] * kv.max_blocks + b];
+}
 
 // The residual values of 32 consecutive columns of one row, asked for before the accumulator is
 // read so that the trip to memory overlaps the tensor-memory load.  False (nothing loaded) if
@@ -150,8 +175,10 @@ __device__ __forceinline__ bool load_residual(float4 (&res)[8], int row, int col
 }
 
 // Write-back of 32 consecutive columns of one row: bias, activation, residual, rounding, store.
+// kv_page, kv_slot: from kv_row_target, used when the chunk holds key or value columns.
 __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, int col0, const EpilogueArgs& ep, int M,
-                                            int N, const float4 (&res)[8], bool have_res) {
+                                            int N, const float4 (&res)[8], bool have_res, int kv_page, int kv_slot,
+                                            int* status) {
     // the chunk's 32 bias values: one load per lane, handed round by shuffles (32 scalar loads per
     // thread were a trip to memory in front of every chunk's arithmetic)
     const int lane = threadIdx.x & 31;
@@ -160,6 +187,36 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, in
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; j++) v[j] = apply_act_fast(__uint_as_float(r[j]) + __shfl_sync(0xffffffffu, my_bias, j), ep.act);
+    if (ep.kv.k_cache && row < M && col0 + 32 > ep.kv.q_cols) {
+        // key / value columns also go straight into the request's page, eight at a time (a head's
+        // size is a multiple of 16, so eight consecutive columns never straddle two heads)
+        if (kv_page < 0 || kv_page >= ep.kv.num_pages) {
+            if (status) atomicOr(status, 8);
+        } else {
+#pragma unroll
+            for (int g8 = 0; g8 < 4; g8++) {
+                const int col = col0 + 8 * g8;
+                if (col >= ep.kv.q_cols && col + 8 <= N) {
+                    const int c = col - ep.kv.q_cols;
+                    const bool is_v = c >= ep.kv.kv_cols;
+                    const int c2 = is_v ? c - ep.kv.kv_cols : c;
+                    const int head = c2 / ep.kv.head_dim, d = c2 % ep.kv.head_dim;
+                    bf16* dst = (is_v ? ep.kv.v_cache : ep.kv.k_cache) + (size_t)kv_page * ep.kv.page_stride +
+                                ((size_t)head * ep.kv.page_size + kv_slot) * ep.kv.head_dim + d;
+                    uint4 pk;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * g8], v[8 * g8 + 1]);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * g8 + 2], v[8 * g8 + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * g8 + 4], v[8 * g8 + 5]);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * g8 + 6], v[8 * g8 + 7]);
+                    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                    *reinterpret_cast<uint4*>(dst) = pk;
+                }
+            }
+        }
+    }
     if (row < M && col0 < N) {
         const bool full = col0 + 32 <= N;
         if (have_res) {

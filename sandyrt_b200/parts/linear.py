@@ -123,6 +123,9 @@ class Linear:
         if isinstance(a, LazyNorm):
             a = a.tensor()
         if self.use_tensor_cores:
-            ops.gemm_tc(a, self.weight, self.bias, out, act=act, residual=residual)
+            fused_kv = kv is not None and kv.head_dim % 16 == 0 and kv.q_cols % 8 == 0
+            ops.gemm_tc(a, self.weight, self.bias, out, act=act, residual=residual, kv=kv if fused_kv else None)
+            if fused_kv:
+                kv.written = True
         else:
             ops.gemm_simt(a, self.weight, self.bias, out, w_out_in=self.w_out_in, act=act, residual=residual)

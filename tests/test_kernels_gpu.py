@@ -497,3 +497,48 @@ def test_gemm_skinny_writes_keys_and_values_into_the_pages():
     ops.check_kernel_status(DEV)
     assert torch.equal(out_a, out_b)
     assert torch.equal(arena_a, arena_b) and float(arena_a.abs().sum()) > 0
+
+
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256, -64, -128, -256, 2128, 2256])
+@pytest.mark.parametrize("H,Hkv,D,ps", [(6, 2, 32, 8), (3, 3, 16, 16), (5, 1, 48, 4)])
+def test_gemm_tc_writes_keys_and_values_into_the_pages(tile_n, H, Hkv, D, ps):
+    """The fused q/k/v product of a prompt step on tcgen05 with the cache write in its write-back:
+    same product, same pages as the product followed by kv_append.  Portions of several requests
+    (one behind a prefix, tokens that cross page edges), column ranges that are no multiple of
+    the kernel's 32-column chunks."""
+    from sandyrt_b200.csrc import ops
+    from sandyrt_b200.parts.linear import KVTarget
+
+    q_cols, kv_cols = H * D, Hkv * D
+    K = 96
+    seqs = [(13, 150), (0, 77), (7, 1), (40, 200)]
+    T = sum(n for _, n in seqs)
+    num_pages = 160
+    g = torch.Generator().manual_seed(0)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    width = max(-(-(b + n) // ps) for b, n in seqs)
+    table = torch.full((len(seqs), width), -1, dtype=torch.int32)
+    tok_seq, tok_pos = [], []
+    for s, (before, n) in enumerate(seqs):
+        for b in range(-(-(before + n) // ps)):
+            table[s, b] = perm.pop()
+        tok_seq += [s] * n
+        tok_pos += list(range(before, before + n))
+    table = table.to(DEV)
+    tok_seq = torch.tensor(tok_seq, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(tok_pos, dtype=torch.int32, device=DEV)
+    a = _rand((T, K), torch.bfloat16, 1)
+    w = _rand((q_cols + 2 * kv_cols, K), torch.bfloat16, 2, scale=0.2)
+    bias = _rand((q_cols + 2 * kv_cols,), torch.bfloat16, 3)
+    arena_a = torch.zeros(num_pages, 2, Hkv, ps, D, dtype=torch.bfloat16, device=DEV)
+    arena_b = torch.zeros_like(arena_a)
+    out_a = torch.empty(T, q_cols + 2 * kv_cols, dtype=torch.bfloat16, device=DEV)
+    out_b = torch.empty_like(out_a)
+    target = KVTarget(arena_a[:, 0], arena_a[:, 1], table, tok_seq, tok_pos, q_cols, kv_cols, D)
+    ops.gemm_tc(a, w, bias, out_a, kv=target, tile_n=tile_n)
+    ops.gemm_tc(a, w, bias, out_b, tile_n=tile_n)
+    ops.kv_append(out_b[:, q_cols:q_cols + kv_cols], out_b[:, q_cols + kv_cols:], arena_b[:, 0], arena_b[:, 1],
+                  table, tok_seq, tok_pos)
+    ops.check_kernel_status(DEV)
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(arena_a, arena_b) and float(arena_a.abs().sum()) > 0
