@@ -44,6 +44,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_decode_bulk": [],
     "decode_program": [],
     "attention_prefill": [],
+    "attention_prefill_tc": [],
     "sampling": [],
 }
 

@@ -295,10 +295,16 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
         LAUNCHES += 1
 
 
+# Heads of 64 go to the tcgen05 kernel; "0" keeps every head size on the mma.sync kernel (for comparisons).
+_PREFILL_TC = os.environ.get("SANDYRT_PREFILL_TC", "1") != "0"
+
+
 def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out, *, n_heads: int,
-                      max_q_len: int, scale: float, window: int = 0) -> None:
+                      max_q_len: int, scale: float, window: int = 0, tc=None) -> None:
     """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).
-    q_start: int32 [S+1] first new token of each request; kv_before: int32 [S]."""
+    q_start: int32 [S+1] first new token of each request; kv_before: int32 [S].
+    tc: True asks for the tcgen05 kernel (heads of 64), False for the mma.sync kernel, None
+    picks the tcgen05 kernel where it takes the shape."""
     _no_record("attention of prompt portions")
     _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
@@ -313,6 +319,16 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
     S = kv_before.numel()
     if q_start.numel() != S + 1 or block_table.shape[0] != S:
         raise KernelError("prefill_attention: q_start, kv_before and block_table disagree on the requests")
+    args = (_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride),
+            _p(block_table), ctypes.c_int(block_table.shape[1]), _p(q_start), _p(kv_before), _p(out),
+            ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len), ctypes.c_int(n_heads),
+            ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
+            ctypes.c_int(num_pages), _p(kernel_status(q.device)), _stream())
+    if tc or (tc is None and _PREFILL_TC and d == 64):
+        code = load_library("attention_prefill_tc").sandy_prefill_attention_tc(*args)
+        if code != -1 or tc:
+            _check(code, f"prefill_attention_tc(H={n_heads},Hkv={hkv},D={d})")
+            return
     lib = load_library("attention_prefill")
     code = lib.sandy_prefill_attention(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
                                        ctypes.c_longlong(page_stride), _p(block_table),
@@ -412,7 +428,7 @@ def check_kernel_status(device) -> None:
         raise KernelError(f"a kernel reported a fault (status {code}: bits 0-2 a barrier wait ran out in the "
                           "tensor-core product, bit 3 a key/value write and bit 4 a key read had no page behind "
                           "it, bits 5-6 a wait ran out in the bulk decode attention, bit 7 in the decode "
-                          "program); the step's output is not valid")
+                          "program, bit 8 in the tcgen05 prefill attention); the step's output is not valid")
 
 
 def tensor_core_gemm_supported(K: int, N: int) -> bool:

@@ -331,8 +331,10 @@ def test_one_far_key_among_hundreds(kernel):
                                                      (12, 12, 64, 16, 0), (6, 2, 64, 16, 0), (5, 1, 80, 4, 0),
                                                      (4, 2, 128, 32, 0), (3, 3, 32, 16, 20), (6, 3, 64, 8, 70),
                                                      (2, 2, 96, 16, 0), (2, 1, 112, 16, 0)])
-def test_prefill_attention_tensor_cores(H, Hkv, D, page_size, window):
-    """Portions that start at 0 and in the middle of a prompt, of 1 to 200 tokens, beside
+@pytest.mark.parametrize("tc", [None, False])
+def test_prefill_attention_tensor_cores(H, Hkv, D, page_size, window, tc):
+    """tc None: heads of 64 on the tcgen05 kernel, the others on the mma.sync kernel; False: all
+    on the mma.sync kernel.  Portions that start at 0 and in the middle of a prompt, of 1 to 200 tokens, beside
     single tokens; tile edges (63/64/65), page edges, windows."""
     from sandyrt_b200.csrc import ops
 
@@ -344,7 +346,7 @@ def test_prefill_attention_tensor_cores(H, Hkv, D, page_size, window):
     q_start = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
     kv_before = torch.tensor([b for b, _ in seqs], dtype=torch.int32, device=DEV)
     ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
-                          max_q_len=max(lens), scale=scale, window=window)
+                          max_q_len=max(lens), scale=scale, window=window, tc=tc)
     ops.check_kernel_status(DEV)
     want = _attention_want(case, H, Hkv, D, scale, window)
     assert not torch.isnan(out).any()
@@ -353,7 +355,8 @@ def test_prefill_attention_tensor_cores(H, Hkv, D, page_size, window):
 
 @pytest.mark.parametrize("H,Hkv,D,page_size,window", [(3, 3, 64, 16, 0), (4, 2, 32, 16, 0), (2, 2, 128, 32, 0),
                                                      (3, 1, 64, 8, 150)])
-def test_prefill_attention_long_portions(H, Hkv, D, page_size, window):
+@pytest.mark.parametrize("tc", [None, False])
+def test_prefill_attention_long_portions(H, Hkv, D, page_size, window, tc):
     """Portions of 256 tokens and more (many key tiles per query tile): a portion from position 0,
     one behind a long prefix, an odd number of tiles, short ones beside them, a window."""
     from sandyrt_b200.csrc import ops
@@ -366,14 +369,15 @@ def test_prefill_attention_long_portions(H, Hkv, D, page_size, window):
     q_start = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
     kv_before = torch.tensor([b for b, _ in seqs], dtype=torch.int32, device=DEV)
     ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
-                          max_q_len=max(lens), scale=scale, window=window)
+                          max_q_len=max(lens), scale=scale, window=window, tc=tc)
     ops.check_kernel_status(DEV)
     want = _attention_want(case, H, Hkv, D, scale, window)
     assert not torch.isnan(out).any()
     assert (out.double().cpu() - want).abs().max().item() < 2e-2
 
 
-def test_prefill_attention_far_key():
+@pytest.mark.parametrize("tc", [None, False])
+def test_prefill_attention_far_key(tc):
     from sandyrt_b200.csrc import ops
 
     H = Hkv = 2
@@ -385,7 +389,7 @@ def test_prefill_attention_far_key():
         q_start = torch.tensor([0, 90, 93], dtype=torch.int32, device=DEV)
         kv_before = torch.tensor([520, 5], dtype=torch.int32, device=DEV)
         ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
-                              max_q_len=90, scale=0.125)
+                              max_q_len=90, scale=0.125, tc=tc)
         v_far = case["dense_v"][0][far].float()
         got = out[:90].view(90, H, D).float().cpu()
         assert (got - v_far).abs().max().item() < 3e-2, f"far key {far}"
@@ -396,7 +400,8 @@ def test_prefill_attention_far_key():
         q_start = torch.tensor([0, 300, 303], dtype=torch.int32, device=DEV)
         kv_before = torch.tensor([310, 5], dtype=torch.int32, device=DEV)
         ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
-                              max_q_len=300, scale=0.125)
+                              max_q_len=300, scale=0.125, tc=tc)
+        ops.check_kernel_status(DEV)
         if far <= 310:          # visible to every query of the portion
             v_far = case["dense_v"][0][far].float()
             got = out[:300].view(300, H, D).float().cpu()
