@@ -164,18 +164,21 @@ def test_gemm_tc_refuses_what_it_cannot_take():
 
 
 # ---- attention over the paged cache ------------------------------------------------------------
-def _paged_case(dtype, H, Hkv, D, page_size, seqs, seed, spike=None):
+def _paged_case(dtype, H, Hkv, D, page_size, seqs, seed, spike=None, runs=()):
     """seqs: list of (tokens already cached, new tokens).  Builds q for the new tokens, dense
     K/V per request, and a cache whose pages are handed out in a shuffled order; the cached
     prefix is written directly, the new tokens' K/V through kv_append.  `spike`: (request,
     key position): that key and every query of the request are scaled so that this one score
-    stands out among hundreds."""
+    stands out among hundreds.  `runs`: requests whose pages follow one another in the cache (the
+    way a pool hands them out to a prompt), instead of lying anywhere."""
     from sandyrt_b200.csrc import ops
 
     g = torch.Generator(device="cpu").manual_seed(seed)
     n_blocks = [-(-(b + n) // page_size) for b, n in seqs]
     num_pages = sum(n_blocks) + 3
-    perm = torch.randperm(num_pages, generator=g).tolist()
+    n_run = sum(n_blocks[s] for s in runs)
+    run_first = 1                                          # runs lie at pages 1 .. n_run, the others anywhere behind
+    perm = (torch.randperm(num_pages - n_run - 1, generator=g) + n_run + 1).tolist() + [0]
     max_blocks = max(n_blocks) + 2
     table = torch.full((len(seqs), max_blocks), -1, dtype=torch.int32)
     arena = torch.full((num_pages, 2, Hkv, page_size, D), float("nan"), dtype=dtype)
@@ -191,7 +194,11 @@ def _paged_case(dtype, H, Hkv, D, page_size, seqs, seed, spike=None):
         k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
         dense_k.append(k); dense_v.append(v); qs.append(q)
         for b in range(n_blocks[s]):
-            table[s, b] = perm.pop()
+            if s in runs:
+                table[s, b] = run_first
+                run_first += 1
+            else:
+                table[s, b] = perm.pop()
         for p in range(before):
             page = table[s, p // page_size]
             arena[page, 0, :, p % page_size] = k[p]
@@ -376,6 +383,37 @@ def test_prefill_attention_long_portions(H, Hkv, D, page_size, window, tc):
     assert (out.double().cpu() - want).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("H,Hkv,page_size,window", [(3, 3, 16, 0), (4, 2, 8, 0), (2, 1, 32, 200), (2, 2, 64, 0),
+                                                   (2, 2, 128, 0)])
+def test_prefill_attention_page_runs(H, Hkv, page_size, window):
+    """Requests whose pages follow one another in the cache beside requests whose pages lie anywhere:
+    the tcgen05 kernel fetches whole key tiles of the former with TMA and the rest (and every
+    request's last, partly filled tile) with copies by its threads.  Portions at position 0 and
+    behind a prefix, aligned to the tiles and not, a far key in a tile that TMA fetched."""
+    from sandyrt_b200.csrc import ops
+
+    D = 64
+    seqs = [(0, 512), (256, 300), (0, 700), (130, 257), (0, 128), (384, 1)]
+    for far in (5, 300):
+        case = _paged_case(torch.bfloat16, H, Hkv, D, page_size, seqs, seed=H + page_size, runs=(0, 1, 4, 5),
+                           spike=(0, far))
+        out = torch.full_like(case["q"], float("nan"))
+        scale = 1.0 / math.sqrt(D)
+        lens = [n for _, n in seqs]
+        q_start = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
+        kv_before = torch.tensor([b for b, _ in seqs], dtype=torch.int32, device=DEV)
+        ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
+                              max_q_len=max(lens), scale=scale, window=window, tc=True)
+        ops.check_kernel_status(DEV)
+        want = _attention_want(case, H, Hkv, D, scale, window)
+        assert not torch.isnan(out).any()
+        assert (out.double().cpu() - want).abs().max().item() < 2e-2
+        if window == 0:
+            v_far = case["dense_v"][0][far].float().repeat_interleave(H // Hkv, dim=0)
+            got = out[max(far, 0):512].view(-1, H, D).float().cpu()
+            assert (got - v_far).abs().max().item() < 3e-2, f"far key {far}"
+
+
 @pytest.mark.parametrize("tc", [None, False])
 def test_prefill_attention_far_key(tc):
     from sandyrt_b200.csrc import ops
@@ -476,7 +514,9 @@ def test_gemm_skinny_writes_keys_and_values_into_the_pages():
     T = sum(n for _, n in seqs)
     num_pages = 32
     g = torch.Generator().manual_seed(0)
-    perm = torch.randperm(num_pages, generator=g).tolist()
+    n_run = sum(n_blocks[s] for s in runs)
+    run_first = 1                                          # runs lie at pages 1 .. n_run, the others anywhere behind
+    perm = (torch.randperm(num_pages - n_run - 1, generator=g) + n_run + 1).tolist() + [0]
     table = torch.full((len(seqs), 8), -1, dtype=torch.int32)
     tok_seq, tok_pos = [], []
     for s, (before, n) in enumerate(seqs):
@@ -520,7 +560,9 @@ def test_gemm_tc_writes_keys_and_values_into_the_pages(tile_n, H, Hkv, D, ps):
     T = sum(n for _, n in seqs)
     num_pages = 160
     g = torch.Generator().manual_seed(0)
-    perm = torch.randperm(num_pages, generator=g).tolist()
+    n_run = sum(n_blocks[s] for s in runs)
+    run_first = 1                                          # runs lie at pages 1 .. n_run, the others anywhere behind
+    perm = (torch.randperm(num_pages - n_run - 1, generator=g) + n_run + 1).tolist() + [0]
     width = max(-(-(b + n) // ps) for b, n in seqs)
     table = torch.full((len(seqs), width), -1, dtype=torch.int32)
     tok_seq, tok_pos = [], []
