@@ -10,7 +10,8 @@ src/device/cuda/CudaPagedTensor.cpp:232-267); growth by ceil(new_len / page_size
 src/server/Session.cpp:552-563); one list of cache groups per model
 (`CacheGroupConfig`, src/server/Session.h:36-41, src/server/Model.cpp:106-111).
 
-What is different here: many requests live at once and share the pools; a request has one
+What is different here: the lowest free page goes out first (so that a prompt's pages tend to
+be a run); many requests live at once and share the pools; a request has one
 block list per *group* (all layers of a group use the same page ids), not one page table
 per tensor; pages of a group whose layers only look back `window` positions are given back
 as soon as the window has passed them; and every request also holds one *state slot*, a
@@ -19,6 +20,7 @@ row index into per-request state of fixed size.
 from __future__ import annotations
 
 import dataclasses
+import heapq
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 from ..parts.base import PagedKVSpec, StateSpec
@@ -39,14 +41,17 @@ class CacheError(Exception):
 
 
 class PagePool:
-    """Page ids 0..num_pages-1 with a LIFO free list (a page just freed is the next one
-    handed out, so tests with few pages reuse them at once)."""
+    """Page ids 0..num_pages-1; the free page with the lowest id is handed out first (the
+    reference's pool is a LIFO list).  A fresh pool hands out 0, 1, 2, ..., and whenever the low
+    end of the pool is free again a request's pages follow one another in the cache: the
+    prompt attention kernel fetches such runs with one copy per tile.  With few pages (the
+    tests) a page just freed is still handed out again at once."""
 
     def __init__(self, num_pages: int):
         if num_pages <= 0:
             raise CacheError("a page pool needs at least one page")
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))
+        self._free: List[int] = list(range(num_pages))      # a heap (an ascending list is one)
         self._held = [False] * num_pages
         self.high_water = 0
 
@@ -61,20 +66,22 @@ class PagePool:
     def allocate(self, n: int) -> List[int]:
         if n > len(self._free):
             raise OutOfPages(f"need {n} pages, {len(self._free)} of {self.num_pages} free")
-        pages = [self._free.pop() for _ in range(n)]
+        pages = [heapq.heappop(self._free) for _ in range(n)]
         for p in pages:
             self._held[p] = True
         self.high_water = max(self.high_water, self.used_pages)
         return pages
 
     def release(self, pages: Sequence[int]) -> None:
+        pages = list(pages)
         for p in pages:
             if not (0 <= p < self.num_pages):
                 raise CacheError(f"page {p} does not belong to this pool")
             if not self._held[p]:
                 raise CacheError(f"page {p} freed twice")
             self._held[p] = False
-            self._free.append(p)
+        for p in pages:
+            heapq.heappush(self._free, p)
 
 
 @dataclasses.dataclass

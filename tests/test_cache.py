@@ -9,6 +9,18 @@ from sandyrt_b200.cache.pages import (FREED, BlockAllocator, CacheError, CacheLa
 from sandyrt_b200.parts.base import PagedKVSpec, StateSpec
 
 
+def test_pool_hands_out_runs():
+    """A fresh pool hands out 0, 1, 2, ...; afterwards always the lowest free pages, in order."""
+    pool = PagePool(16)
+    a = pool.allocate(6)
+    b = pool.allocate(4)
+    assert a == [0, 1, 2, 3, 4, 5] and b == [6, 7, 8, 9]
+    pool.release(a)
+    assert pool.allocate(4) == [0, 1, 2, 3]
+    pool.release(b)
+    assert pool.allocate(6) == [4, 5, 6, 7, 8, 9]
+
+
 def _alloc(specs, pages, page_size=16, max_requests=4):
     layout = CacheLayout.from_specs(specs, page_size)
     return BlockAllocator(layout, [pages] * len(layout.groups), max_requests)
@@ -19,7 +31,7 @@ def test_pool_reuses_last_freed_first_and_detects_double_free():
     a = pool.allocate(3)
     assert sorted(a) == [0, 1, 2] and pool.free_pages == 1
     pool.release([a[1]])
-    assert pool.allocate(1) == [a[1]]              # LIFO: the page just freed comes back
+    assert pool.allocate(1) == [a[1]]              # the page just freed comes back (it is the lowest free one)
     with pytest.raises(OutOfPages):
         pool.allocate(2)
     assert pool.free_pages == 1                    # a failed allocation takes nothing

@@ -514,9 +514,7 @@ def test_gemm_skinny_writes_keys_and_values_into_the_pages():
     T = sum(n for _, n in seqs)
     num_pages = 32
     g = torch.Generator().manual_seed(0)
-    n_run = sum(n_blocks[s] for s in runs)
-    run_first = 1                                          # runs lie at pages 1 .. n_run, the others anywhere behind
-    perm = (torch.randperm(num_pages - n_run - 1, generator=g) + n_run + 1).tolist() + [0]
+    perm = torch.randperm(num_pages, generator=g).tolist()
     table = torch.full((len(seqs), 8), -1, dtype=torch.int32)
     tok_seq, tok_pos = [], []
     for s, (before, n) in enumerate(seqs):
@@ -560,9 +558,7 @@ def test_gemm_tc_writes_keys_and_values_into_the_pages(tile_n, H, Hkv, D, ps):
     T = sum(n for _, n in seqs)
     num_pages = 160
     g = torch.Generator().manual_seed(0)
-    n_run = sum(n_blocks[s] for s in runs)
-    run_first = 1                                          # runs lie at pages 1 .. n_run, the others anywhere behind
-    perm = (torch.randperm(num_pages - n_run - 1, generator=g) + n_run + 1).tolist() + [0]
+    perm = torch.randperm(num_pages, generator=g).tolist()
     width = max(-(-(b + n) // ps) for b, n in seqs)
     table = torch.full((len(seqs), width), -1, dtype=torch.int32)
     tok_seq, tok_pos = [], []
