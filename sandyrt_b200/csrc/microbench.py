@@ -2,11 +2,16 @@
 
     python -m sandyrt_b200.csrc.microbench decode-attention [--heads 12] [--head-dim 64] [--page-size 16]
     python -m sandyrt_b200.csrc.microbench gemm [--rows 2048] [--width 768] [--inner 3072] [--k-sweep]
+    python -m sandyrt_b200.csrc.microbench prefill-attention [--heads 12] [--page-size 16] [--shape 2x1024+0 ...]
 
 decode-attention: the register kernel and the bulk-copy kernel of single-token attention on
 several (tokens, context) shapes.  Each timing replays a graph of one launch per distinct cache
 (enough caches to exceed L2), so neither the host's launch cost nor a warm L2 is in the number;
 bytes are the keys and values a launch must read.
+
+prefill-attention: the mma.sync kernel and the tcgen05 kernel of prompt attention (heads of 64)
+on shapes given as REQUESTSxNEW+CACHED, with the requests' pages one after another in the cache
+and scattered; FLOP are those of the causal part (4 * head * keys seen, per query and head).
 """
 from __future__ import annotations
 
@@ -117,6 +122,47 @@ def gemm(a) -> int:
     return 0
 
 
+def prefill_attention(a) -> int:
+    import math
+
+    dev = "cuda:0"
+    H, D, ps = a.heads, 64, a.page_size
+    print(f"prefill attention, {H} heads of {D}, pages of {ps}; us per launch and TFLOP/s of the causal part")
+    for shape in a.shape:
+        reqs, rest = shape.split("x")
+        new, cached = rest.split("+")
+        n_seqs, q_len, before = int(reqs), int(new), int(cached)
+        L = before + q_len
+        nb = -(-L // ps)
+        num_pages = n_seqs * nb + 1
+        g = torch.Generator(device=dev).manual_seed(0)
+        arena = torch.randn(num_pages, 2, H, ps, D, device=dev, generator=g).to(torch.bfloat16)
+        kc, vc = arena[:, 0], arena[:, 1]
+        T = n_seqs * q_len
+        q = torch.randn(T, H * D, device=dev, generator=g).to(torch.bfloat16)
+        q_start = torch.arange(0, T + 1, q_len, dtype=torch.int32, device=dev)
+        kv_before = torch.full((n_seqs,), before, dtype=torch.int32, device=dev)
+        flops = 4.0 * n_seqs * H * D * sum(before + i + 1 for i in range(q_len))
+        tables = {"runs": torch.arange(n_seqs * nb, device=dev, dtype=torch.int32).view(n_seqs, nb).contiguous(),
+                  "scattered": torch.randperm(num_pages - 1, device=dev, generator=g).to(torch.int32)[:n_seqs * nb]
+                  .view(n_seqs, nb).contiguous()}
+        outs = {}
+        for pages, table in tables.items():
+            for name, tc in (("mma.sync", False), ("tcgen05", True)):
+                out = torch.zeros_like(q)
+
+                def go(l, table=table, tc=tc, out=out):
+                    ops.prefill_attention(q, kc, vc, table, q_start, kv_before, out, n_heads=H, max_q_len=q_len,
+                                          scale=1 / math.sqrt(D), tc=tc)
+                us = _time_graph(go, a.launches)
+                ops.check_kernel_status(dev)
+                outs[name] = out.float()
+                print(f"  {shape:>12} pages {pages:>9} {name:>8}: {us:7.1f} us  {flops / us / 1e6:6.0f} TFLOP/s", flush=True)
+            print(f"  {'':>12} largest difference between the two kernels: "
+                  f"{(outs['tcgen05'] - outs['mma.sync']).abs().max().item():.4f}")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="sandyrt_b200.csrc.microbench")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -131,6 +177,13 @@ def main(argv=None) -> int:
     g.add_argument("--inner", type=int, default=3072)
     g.add_argument("--k-sweep", action="store_true", help="also time the q/k/v output size at several K")
     g.set_defaults(fn=gemm)
+    pa = sub.add_parser("prefill-attention")
+    pa.add_argument("--heads", type=int, default=12)
+    pa.add_argument("--page-size", type=int, default=16)
+    pa.add_argument("--launches", type=int, default=20, help="launches per timed graph")
+    pa.add_argument("--shape", nargs="+", default=["2x1024+0", "8x256+0", "4x512+512", "16x128+0", "2x2048+0", "1x8192+0"],
+                    help="REQUESTSxNEW+CACHED")
+    pa.set_defaults(fn=prefill_attention)
     a = ap.parse_args(argv)
     return a.fn(a)
 
