@@ -164,13 +164,14 @@ def test_gemm_tc_refuses_what_it_cannot_take():
 
 
 # ---- attention over the paged cache ------------------------------------------------------------
-def _paged_case(dtype, H, Hkv, D, page_size, seqs, seed, spike=None, runs=()):
+def _paged_case(dtype, H, Hkv, D, page_size, seqs, seed, spike=None, runs=(), swap=None):
     """seqs: list of (tokens already cached, new tokens).  Builds q for the new tokens, dense
     K/V per request, and a cache whose pages are handed out in a shuffled order; the cached
     prefix is written directly, the new tokens' K/V through kv_append.  `spike`: (request,
     key position): that key and every query of the request are scaled so that this one score
     stands out among hundreds.  `runs`: requests whose pages follow one another in the cache (the
-    way a pool hands them out to a prompt), instead of lying anywhere."""
+    way a pool hands them out to a prompt), instead of lying anywhere; `swap`: (request, i, j): its
+    blocks i and j change pages, which breaks a run inside a key tile."""
     from sandyrt_b200.csrc import ops
 
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -199,6 +200,9 @@ def _paged_case(dtype, H, Hkv, D, page_size, seqs, seed, spike=None, runs=()):
                 run_first += 1
             else:
                 table[s, b] = perm.pop()
+        if swap is not None and swap[0] == s:
+            i, j = swap[1], swap[2]
+            table[s, i], table[s, j] = table[s, j].clone(), table[s, i].clone()
         for p in range(before):
             page = table[s, p // page_size]
             arena[page, 0, :, p % page_size] = k[p]
@@ -412,6 +416,30 @@ def test_prefill_attention_page_runs(H, Hkv, page_size, window):
             v_far = case["dense_v"][0][far].float().repeat_interleave(H // Hkv, dim=0)
             got = out[max(far, 0):512].view(-1, H, D).float().cpu()
             assert (got - v_far).abs().max().item() < 3e-2, f"far key {far}"
+
+
+def test_prefill_attention_broken_run_and_long_tables():
+    """A run of pages with two pages exchanged (tiles with the break come by the threads' copies,
+    the others by TMA); a block table longer than the kernel keeps in shared memory; more key tiles
+    than it keeps run marks for."""
+    from sandyrt_b200.csrc import ops
+
+    H, Hkv, D = 2, 1, 64
+    for page_size, seqs, runs, swap in ((16, [(0, 600), (100, 3)], (0,), (0, 3, 20)),
+                                        (8, [(9000, 130), (0, 64)], (0, 1), None),
+                                        (16, [(16500, 130)], (0,), None)):
+        case = _paged_case(torch.bfloat16, H, Hkv, D, page_size, seqs, seed=page_size, runs=runs, swap=swap)
+        out = torch.full_like(case["q"], float("nan"))
+        scale = 1.0 / math.sqrt(D)
+        lens = [n for _, n in seqs]
+        q_start = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
+        kv_before = torch.tensor([b for b, _ in seqs], dtype=torch.int32, device=DEV)
+        ops.prefill_attention(case["q"], case["kc"], case["vc"], case["table"], q_start, kv_before, out, n_heads=H,
+                              max_q_len=max(lens), scale=scale, tc=True)
+        ops.check_kernel_status(DEV)
+        want = _attention_want(case, H, Hkv, D, scale, 0)
+        assert not torch.isnan(out).any()
+        assert (out.double().cpu() - want).abs().max().item() < 2e-2
 
 
 @pytest.mark.parametrize("tc", [None, False])
