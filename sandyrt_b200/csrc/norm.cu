@@ -8,6 +8,8 @@
 // three times.  Here a row belongs to ONE WARP and lives in its registers between the passes
 // (rows up to 4096 wide; wider rows take the block-per-row kernel that stages the row in
 // shared memory), so the two reductions are warp shuffles and a block handles eight rows.
+// Where the width is a multiple of 4 and the rows are aligned, a lane moves its four
+// consecutive elements with one 16-byte (float) or 8-byte (bfloat16) access.
 //
 // `rows` (optional) selects which input rows are normalised: output row r is the norm of
 // input row rows[r].  The engine uses it to run the final norm only at the positions
@@ -18,11 +20,33 @@ namespace {
 
 constexpr int ROWS_PER_BLOCK = 8;
 
-// VEC: elements per lane per round (4 floats or 8 halfs = 16 bytes); NV: rounds (width <= 32*4*NV)
+// Four consecutive elements with one access.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x), b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<const uint32_t*>(&a);
+    t.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+
+// A lane holds 4 consecutive elements per round; NV: rounds (width <= 32*4*NV).  vec: the width is
+// a multiple of 4 and every pointer is aligned for 4-element accesses.
 template <typename TI, typename TW, typename TO, int NV>
 __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
 layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, const TW* __restrict__ beta,
-                      TO* __restrict__ out, const int* __restrict__ rows, int n_rows, int width, float eps) {
+                      TO* __restrict__ out, const int* __restrict__ rows, int n_rows, int width, float eps, int vec) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -35,11 +59,14 @@ layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, co
 #pragma unroll
     for (int i = 0; i < NV; i++) {
         const int e = (i * 32 + lane) * 4;
+        if (vec) {
+            if (e < width) load4(xr + e, v[i]);
+            else v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.0f;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            v[i][j] = (e + j < width) ? to_f32(xr[e + j]) : 0.0f;
-            s += v[i][j];
+            for (int j = 0; j < 4; j++) v[i][j] = (e + j < width) ? to_f32(xr[e + j]) : 0.0f;
         }
+        s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
     }
     const float mean = warp_sum(s) / (float)width;
     float q = 0.0f;
@@ -57,12 +84,23 @@ layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, co
 #pragma unroll
     for (int i = 0; i < NV; i++) {
         const int e = (i * 32 + lane) * 4;
+        if (vec) {
+            if (e < width) {
+                float g[4], b[4] = {0.0f, 0.0f, 0.0f, 0.0f}, y[4];
+                load4(gamma + e, g);
+                if (beta) load4(beta + e, b);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            if (e + j < width) {
-                float y = (v[i][j] - mean) * inv * to_f32(gamma[e + j]);
-                if (beta) y += to_f32(beta[e + j]);
-                orow[e + j] = from_f32<TO>(y);
+                for (int j = 0; j < 4; j++) y[j] = (v[i][j] - mean) * inv * g[j] + b[j];
+                store4(orow + e, y);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (e + j < width) {
+                    float y = (v[i][j] - mean) * inv * to_f32(gamma[e + j]);
+                    if (beta) y += to_f32(beta[e + j]);
+                    orow[e + j] = from_f32<TO>(y);
+                }
             }
         }
     }
@@ -105,11 +143,15 @@ template <typename TI, typename TW, typename TO>
 int launch(const void* x, const void* gamma, const void* beta, void* out, const int* rows, int n_rows, int width,
            float eps, cudaStream_t stream) {
     const dim3 grid((n_rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), block(ROWS_PER_BLOCK * 32);
+    auto aligned = [](const void* p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0; };
+    const int vec = width % 4 == 0 && aligned(x, 4 * sizeof(TI)) && aligned(gamma, 4 * sizeof(TW)) &&
+                    (!beta || aligned(beta, 4 * sizeof(TW))) && aligned(out, 4 * sizeof(TO));
 #define WARP_CASE(NV)                                                                                          \
     if (width <= 128 * NV)                                                                                     \
         return sandy_launch(layernorm_warp_kernel<TI, TW, TO, NV>, grid, block, 0, stream, (const TI*)x,       \
-                            (const TW*)gamma, (const TW*)beta, (TO*)out, rows, n_rows, width, eps)
-    WARP_CASE(1); WARP_CASE(2); WARP_CASE(4); WARP_CASE(8); WARP_CASE(16); WARP_CASE(32);
+                            (const TW*)gamma, (const TW*)beta, (TO*)out, rows, n_rows, width, eps, vec)
+    WARP_CASE(1); WARP_CASE(2); WARP_CASE(3); WARP_CASE(4); WARP_CASE(6); WARP_CASE(8); WARP_CASE(12);
+    WARP_CASE(16); WARP_CASE(24); WARP_CASE(32);
 #undef WARP_CASE
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return SANDY_ERR_UNSUPPORTED;
