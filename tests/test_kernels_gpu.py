@@ -317,9 +317,11 @@ def test_one_far_key_among_hundreds(kernel):
 
     H = Hkv = 2
     D = 64
-    for far in (0, 15, 16, 255, 256, 399, 511, 640):
+    # pages of 16: the request's block table fits the decode kernel's registers; pages of 4: it does not
+    for far, ps in ((0, 16), (15, 16), (16, 16), (255, 16), (256, 16), (399, 16), (511, 16), (640, 16),
+                    (0, 4), (255, 4), (257, 4), (640, 4)):
         seqs = [(641, 1), (5, 1)]
-        case = _paged_case(torch.float32, H, Hkv, D, 16, seqs, seed=far, spike=(0, far))
+        case = _paged_case(torch.float32, H, Hkv, D, ps, seqs, seed=far, spike=(0, far))
         out = torch.full_like(case["q"], float("nan"))
         if kernel == "general":
             ops.paged_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"],
