@@ -317,7 +317,7 @@ def test_one_far_key_among_hundreds(kernel):
 
     H = Hkv = 2
     D = 64
-    # pages of 16: the request's block table fits the decode kernel's registers; pages of 4: it does not
+    # pages of 16 and pages of 4 (a block table of 161 entries)
     for far, ps in ((0, 16), (15, 16), (16, 16), (255, 16), (256, 16), (399, 16), (511, 16), (640, 16),
                     (0, 4), (255, 4), (257, 4), (640, 4)):
         seqs = [(641, 1), (5, 1)]
