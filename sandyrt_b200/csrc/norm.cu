@@ -150,8 +150,8 @@ int launch(const void* x, const void* gamma, const void* beta, void* out, const 
     if (width <= 128 * NV)                                                                                     \
         return sandy_launch(layernorm_warp_kernel<TI, TW, TO, NV>, grid, block, 0, stream, (const TI*)x,       \
                             (const TW*)gamma, (const TW*)beta, (TO*)out, rows, n_rows, width, eps, vec)
-    WARP_CASE(1); WARP_CASE(2); WARP_CASE(3); WARP_CASE(4); WARP_CASE(6); WARP_CASE(8); WARP_CASE(12);
-    WARP_CASE(16); WARP_CASE(24); WARP_CASE(32);
+    WARP_CASE(1); WARP_CASE(2); WARP_CASE(4); WARP_CASE(6); WARP_CASE(8); WARP_CASE(12); WARP_CASE(16);
+    WARP_CASE(32);
 #undef WARP_CASE
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return SANDY_ERR_UNSUPPORTED;
