@@ -84,7 +84,7 @@ struct NormArgs {
 // lane that hold a row during the fused norm (K <= 128 * RV); sized to K so that registers,
 // and with them the number of resident blocks, are not wasted on short rows.
 template <int MT, typename TC, bool FUSE_LN, int UNROLL, int RV>
-__global__ void __launch_bounds__(WARPS * 32, (UNROLL == 4 && RV <= 8 && MT == 1) ? 3 : 1)
+__global__ void __launch_bounds__(WARPS * 32, (UNROLL == 4 && RV <= 8 && MT == 1) ? 3 : ((MT > 1 && !FUSE_LN) ? 2 : 1))
 gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __restrict__ w,
                    const bf16* __restrict__ bias, const float* residual, TC* out, int M, int N, int K, int lda,
                    int ldw, int ldr, int ldc, int act, KVWrite kv) {
