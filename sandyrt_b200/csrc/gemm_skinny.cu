@@ -83,8 +83,11 @@ struct NormArgs {
 // flight per round (chosen so that a warp's whole K slice is one or two rounds).  RV: float4 per
 // lane that hold a row during the fused norm (K <= 128 * RV); sized to K so that registers,
 // and with them the number of resident blocks, are not wasted on short rows.
+// Blocks an SM: three for the one-tile form with short K slices; two for the multi-tile form with
+// short K slices (left alone it takes 216 registers, one block an SM, and a product of 288 column
+// groups runs in two waves); one otherwise (long K: few column groups, a block an SM at most).
 template <int MT, typename TC, bool FUSE_LN, int UNROLL, int RV>
-__global__ void __launch_bounds__(WARPS * 32, (UNROLL == 4 && RV <= 8 && MT == 1) ? 3 : ((MT > 1 && !FUSE_LN) ? 2 : 1))
+__global__ void __launch_bounds__(WARPS * 32, (UNROLL == 4 && RV <= 8 && MT == 1) ? 3 : ((MT > 1 && !FUSE_LN && UNROLL == 4) ? 2 : 1))
 gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __restrict__ w,
                    const bf16* __restrict__ bias, const float* residual, TC* out, int M, int N, int K, int lda,
                    int ldw, int ldr, int ldc, int act, KVWrite kv) {
