@@ -68,6 +68,21 @@ layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, co
         }
         s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
     }
+    // gain and offset are asked for now, beside the row, not after the two reductions
+    constexpr bool EARLY = NV <= 8;
+    float g[EARLY ? NV : 1][4], b[EARLY ? NV : 1][4];
+    if (EARLY && vec) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int e = (i * 32 + lane) * 4;
+            g[i][0] = g[i][1] = g[i][2] = g[i][3] = 0.0f;
+            b[i][0] = b[i][1] = b[i][2] = b[i][3] = 0.0f;
+            if (e < width) {
+                load4(gamma + e, g[i]);
+                if (beta) load4(beta + e, b[i]);
+            }
+        }
+    }
     const float mean = warp_sum(s) / (float)width;
     float q = 0.0f;
 #pragma unroll
@@ -86,11 +101,16 @@ layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, co
         const int e = (i * 32 + lane) * 4;
         if (vec) {
             if (e < width) {
-                float g[4], b[4] = {0.0f, 0.0f, 0.0f, 0.0f}, y[4];
-                load4(gamma + e, g);
-                if (beta) load4(beta + e, b);
+                float gg[4], bb[4] = {0.0f, 0.0f, 0.0f, 0.0f}, y[4];
+                if (EARLY) {
 #pragma unroll
-                for (int j = 0; j < 4; j++) y[j] = (v[i][j] - mean) * inv * g[j] + b[j];
+                    for (int j = 0; j < 4; j++) { gg[j] = g[i][j]; bb[j] = b[i][j]; }
+                } else {
+                    load4(gamma + e, gg);
+                    if (beta) load4(beta + e, bb);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) y[j] = (v[i][j] - mean) * inv * gg[j] + bb[j];
                 store4(orow + e, y);
             }
         } else {
