@@ -50,6 +50,10 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 __device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
 // weights are read once: do not let them push the activations out of L1
 __device__ __forceinline__ uint4 ldg16_stream(const bf16* p) {
     uint4 v;
@@ -125,7 +129,19 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
         wn[u] = (n_ok && c_begin + u < c_end && k < K) ? ldg16_stream(wrow + k) : zero;
     }
 
-    // Everything above touched only the weight, which no kernel writes.  From here on the
+    // The norm's gain and offset are weights too: they are copied into shared memory now, so that
+    // they are not a trip to memory between a row's statistics and its normalised values.
+    bf16* g_sm = xs + (size_t)MT * 16 * xs_ld;           // [K], then the offset [K]
+    bf16* b_sm = g_sm + K;
+    if (FUSE_LN) {
+        for (int k = threadIdx.x * 8; k < K; k += WARPS * 32 * 8) {
+            cp_async16(g_sm + k, norm.gamma + k);
+            if (norm.beta) cp_async16(b_sm + k, norm.beta + k);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+
+    // Everything above touched only weights, which no kernel writes.  From here on the
     // activations are read: the kernels before this one must have finished.
     pdl_launch_dependents();
     pdl_wait();
@@ -143,6 +159,8 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
     }
 
     if (FUSE_LN) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();            // gain and offset are in shared memory
         // warp per row; the row lives in registers between the passes
         for (int r = warp; r < MT * 16; r += WARPS) {
             bf16* dst = xs + (size_t)r * xs_ld;
@@ -174,13 +192,13 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
             for (int i = 0; i < RV; i++) {
                 const int k = (i * 32 + lane) * 4;
                 if (k < K) {
-                    const uint2 gm = *reinterpret_cast<const uint2*>(norm.gamma + k);
+                    const uint2 gm = *reinterpret_cast<const uint2*>(g_sm + k);
                     const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gm);
                     const float2 g01 = __bfloat1622float2(gh[0]), g23 = __bfloat1622float2(gh[1]);
                     float y0 = (v[i].x - mean) * inv * g01.x, y1 = (v[i].y - mean) * inv * g01.y;
                     float y2 = (v[i].z - mean) * inv * g23.x, y3 = (v[i].w - mean) * inv * g23.y;
                     if (norm.beta) {
-                        const uint2 bm = *reinterpret_cast<const uint2*>(norm.beta + k);
+                        const uint2 bm = *reinterpret_cast<const uint2*>(b_sm + k);
                         const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bm);
                         const float2 b01 = __bfloat1622float2(bh[0]), b23 = __bfloat1622float2(bh[1]);
                         y0 += b01.x; y1 += b01.y; y2 += b23.x; y3 += b23.y;
@@ -274,7 +292,7 @@ int launch2(const void* a, const NormArgs& norm, const void* w, const void* bias
             int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act, int out_dtype, const KVWrite& kv,
             cudaStream_t stream) {
     const unsigned blocks = (unsigned)((N + COLS - 1) / COLS);
-    const size_t smem = FUSE_LN ? (size_t)MT * 16 * (K + XPAD) * sizeof(bf16) : 0;
+    const size_t smem = FUSE_LN ? ((size_t)MT * 16 * (K + XPAD) + 2 * (size_t)K) * sizeof(bf16) : 0;   // rows, gain, offset
     if (out_dtype == SANDY_F32) {
         auto kern = gemm_skinny_kernel<MT, float, FUSE_LN, UNROLL, RV>;
         if (smem > 40 * 1024) {
@@ -351,7 +369,7 @@ SANDY_API int sandy_gemm_skinny(const void* a, const float* x, int ldx, const vo
     NormArgs norm{x, (const bf16*)gamma, (const bf16*)beta, ldx, eps};
     if (fuse) {
         if (!gamma || M > 16 || K > MAX_ROW_VEC * 128 || ldx % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) ||
-            (reinterpret_cast<uintptr_t>(gamma) & 7) || (beta && (reinterpret_cast<uintptr_t>(beta) & 7)))
+            (reinterpret_cast<uintptr_t>(gamma) & 15) || (beta && (reinterpret_cast<uintptr_t>(beta) & 15)))
             return SANDY_ERR_UNSUPPORTED;
     } else {
         if (lda % 8 != 0 || (reinterpret_cast<uintptr_t>(a) & 15)) return SANDY_ERR_UNSUPPORTED;

@@ -592,7 +592,8 @@ def skinny_norm_fusable(lazy, K: int) -> bool:
             and gamma.dtype == torch.bfloat16 and lazy.out_dtype == torch.bfloat16
             and lazy.x.dtype == torch.float32 and lazy.x.shape[0] <= SKINNY_NORM_MAX_ROWS
             and K <= SKINNY_NORM_MAX_K and lazy.x.stride(1) == 1 and lazy.x.stride(0) % 4 == 0
-            and lazy.x.data_ptr() % 16 == 0)
+            and lazy.x.data_ptr() % 16 == 0 and gamma.data_ptr() % 16 == 0
+            and (getattr(norm, "beta", None) is None or norm.beta.data_ptr() % 16 == 0))
 
 
 def gemm_skinny(a, w, bias, out, *, act=None, residual=None, norm=None, kv=None) -> None:
