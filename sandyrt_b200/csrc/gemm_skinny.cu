@@ -141,10 +141,22 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
 
+    // The write-back at the end gives output (m, j) to thread m * COLS + j (further rows of a
+    // multi-tile product to the same thread, 32 rows on): the bias of its column is asked for now ...
+    const int my_col = n0 + (int)(threadIdx.x % COLS);
+    const float my_bias = (bias && my_col < N) ? __bfloat162float(bias[my_col]) : 0.0f;
+
     // Everything above touched only weights, which no kernel writes.  From here on the
     // activations are read: the kernels before this one must have finished.
     pdl_launch_dependents();
     pdl_wait();
+
+    // ... and, for the one-tile product, the residual value it will add: neither is then a trip to
+    // memory behind the sums.  (out may be the residual itself: each element is read and written by
+    // one thread only.)
+    float my_res = 0.0f;
+    if (MT == 1 && residual && threadIdx.x < 16 * COLS && (int)(threadIdx.x / COLS) < M && my_col < N)
+        my_res = residual[(size_t)(threadIdx.x / COLS) * ldr + my_col];
 
     // The page this thread's key/value element goes to (two dependent loads): asked for now,
     // needed only in the write-back.
@@ -260,9 +272,9 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
         float v = partial[0][m][j];
 #pragma unroll
         for (int wi = 1; wi < WARPS; wi++) v += partial[wi][m][j];
-        if (bias) v += __bfloat162float(bias[col]);
+        v += my_bias;
         v = apply_act(v, act);
-        if (residual) v += residual[(size_t)m * ldr + col];
+        if (residual) v += MT == 1 ? my_res : residual[(size_t)m * ldr + col];
         out[(size_t)m * ldc + col] = from_f32<TC>(v);
         if (kv.k_cache && col >= kv.q_cols) {
             // a key or value element: straight into the request's page
