@@ -173,7 +173,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     __shared__ float s_max[2][2][BM];   // the maxima a row's two threads tell each other (two copies, used in turn)
     __shared__ float s_sum[2][BM];      // ... and at the end their sums
 
-    pdl_wait();
+    // Which tokens and pages a block works on is written by the host before the step; only q and the
+    // caches are the predecessor's output.  So the set-up below (barriers, tensor memory, the
+    // request's block table, the run marks) runs while the kernel before is still finishing.
     const int s = blockIdx.z, h = blockIdx.y;
     const int qs = q_start[s];
     const int q_len = q_start[s + 1] - qs;
@@ -237,6 +239,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         __syncthreads();
     }
     const uint32_t tmem_base = tmem_slot;
+    pdl_wait();             // from here on q and the caches are read
 
     // ---- copies ---------------------------------------------------------------------------
     // A tile row is 128 bytes (64 bfloat16); 16-byte piece c of row r lies at piece c ^ (r & 7).
