@@ -48,9 +48,25 @@ __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
 layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, const TW* __restrict__ beta,
                       TO* __restrict__ out, const int* __restrict__ rows, int n_rows, int width, float eps, int vec) {
     pdl_launch_dependents();
-    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * ROWS_PER_BLOCK + warp;
+    // Gain and offset are weights, which no kernel writes: they are asked for before the wait for
+    // the kernel that produces x, not after the two reductions.
+    constexpr bool EARLY = NV <= 8;
+    float g[EARLY ? NV : 1][4], b[EARLY ? NV : 1][4];
+    if (EARLY && vec && r < n_rows) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int e = (i * 32 + lane) * 4;
+            g[i][0] = g[i][1] = g[i][2] = g[i][3] = 0.0f;
+            b[i][0] = b[i][1] = b[i][2] = b[i][3] = 0.0f;
+            if (e < width) {
+                load4(gamma + e, g[i]);
+                if (beta) load4(beta + e, b[i]);
+            }
+        }
+    }
+    pdl_wait();
     if (r >= n_rows) return;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     const TI* xr = x + src * width;
@@ -67,21 +83,6 @@ layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, co
             for (int j = 0; j < 4; j++) v[i][j] = (e + j < width) ? to_f32(xr[e + j]) : 0.0f;
         }
         s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
-    }
-    // gain and offset are asked for now, beside the row, not after the two reductions
-    constexpr bool EARLY = NV <= 8;
-    float g[EARLY ? NV : 1][4], b[EARLY ? NV : 1][4];
-    if (EARLY && vec) {
-#pragma unroll
-        for (int i = 0; i < NV; i++) {
-            const int e = (i * 32 + lane) * 4;
-            g[i][0] = g[i][1] = g[i][2] = g[i][3] = 0.0f;
-            b[i][0] = b[i][1] = b[i][2] = b[i][3] = 0.0f;
-            if (e < width) {
-                load4(gamma + e, g[i]);
-                if (beta) load4(beta + e, b[i]);
-            }
-        }
     }
     const float mean = warp_sum(s) / (float)width;
     float q = 0.0f;
