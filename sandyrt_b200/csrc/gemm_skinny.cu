@@ -348,6 +348,109 @@ int launch(const void* a, const NormArgs& norm, const void* w, const void* bias,
     return launch1<MT, FUSE_LN, 16>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
 }
 
+// ---- a vocabulary projection: up to 16 rows, very many columns, nothing fused -------------------
+// The kernel above gives every 8 columns a block of eight warps that split K: for 50,257 columns
+// that is 6,283 short-lived blocks, three of them on an SM at a time, each with 12 KB of weights in
+// flight, and the product runs at half the memory's speed.  Here a WARP owns a group of 8 columns
+// with all of K (no sums across warps, no barrier per group) and walks on to further groups; the
+// rows are staged in shared memory once per block, and a warp always has the next eight 16-byte
+// pieces of its weight rows (of this group or already of the next) on their way.  Same operand
+// pairing as above; a row's result does not depend on the other rows.
+constexpr int WALK_ROUND = 8;            // 16-byte weight pieces a lane keeps in flight
+constexpr int WALK_MIN_GROUPS = 2048;    // from this many column groups on
+constexpr int WALK_MAX_K = 2048;
+
+template <typename TC>
+__global__ void __launch_bounds__(WARPS * 32, 2)
+gemm_skinny_walk_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TC* __restrict__ out, int M, int N,
+                        int K, int lda, int ldw, int ldc) {
+    extern __shared__ __align__(16) uint8_t xs_raw[];
+    bf16* xs = reinterpret_cast<bf16*>(xs_raw);          // [16][K + XPAD]
+    const int xs_ld = K + XPAD;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int chunks = (K + KCHUNK - 1) / KCHUNK;
+    const int groups = (N + COLS - 1) / COLS;
+    const int stride = (int)gridDim.x * WARPS;
+    int grp = (int)blockIdx.x * WARPS + warp;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    uint4 wn[WALK_ROUND];
+    auto load_round = [&](int grp_, int c0) {
+        const int n = grp_ * COLS + g;
+        const bool n_ok = grp_ < groups && n < N;
+        const bf16* wrow = w + (size_t)(n_ok ? n : 0) * ldw;
+#pragma unroll
+        for (int u = 0; u < WALK_ROUND; u++) {
+            const int k = (c0 + u) * KCHUNK + t * 8;
+            wn[u] = (n_ok && c0 + u < chunks && k < K) ? ldg16_stream(wrow + k) : zero;
+        }
+    };
+    load_round(grp, 0);          // weights: no kernel writes them
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pieces = K / 8;
+    for (int idx = threadIdx.x; idx < 16 * pieces; idx += WARPS * 32) {
+        const int r = idx / pieces, c8 = idx % pieces;
+        *reinterpret_cast<uint4*>(xs + (size_t)r * xs_ld + c8 * 8) = r < M ? ldg16(a + (size_t)r * lda + c8 * 8) : zero;
+    }
+    __syncthreads();
+
+    for (; grp < groups; grp += stride) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int c0 = 0; c0 < chunks; c0 += WALK_ROUND) {
+            uint4 wv[WALK_ROUND];
+#pragma unroll
+            for (int u = 0; u < WALK_ROUND; u++) wv[u] = wn[u];
+            if (c0 + WALK_ROUND < chunks) load_round(grp, c0 + WALK_ROUND);
+            else load_round(grp + stride, 0);
+#pragma unroll
+            for (int u = 0; u < WALK_ROUND; u++) {
+                if (c0 + u >= chunks) break;          // the same for every lane: the warp multiplies together
+                const int k = (c0 + u) * KCHUNK + t * 8;
+                const bool k_ok = k < K;               // a lane past K (a last, shorter chunk) feeds zeros
+                const uint4 x0 = k_ok ? *reinterpret_cast<const uint4*>(xs + (size_t)g * xs_ld + k) : zero;
+                const uint4 x1 = k_ok ? *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8) * xs_ld + k) : zero;
+                mma_bf16(acc, x0.x, x1.x, x0.y, x1.y, wv[u].x, wv[u].y);
+                mma_bf16(acc, x0.z, x1.z, x0.w, x1.w, wv[u].z, wv[u].w);
+            }
+        }
+        // C fragment: c0,c1 = (row g, columns 2t, 2t+1); c2,c3 = (row g+8, same columns)
+        const int col = grp * COLS + 2 * t;
+        if (g < M) {
+            if (col < N) out[(size_t)g * ldc + col] = from_f32<TC>(acc[0]);
+            if (col + 1 < N) out[(size_t)g * ldc + col + 1] = from_f32<TC>(acc[1]);
+        }
+        if (g + 8 < M) {
+            if (col < N) out[(size_t)(g + 8) * ldc + col] = from_f32<TC>(acc[2]);
+            if (col + 1 < N) out[(size_t)(g + 8) * ldc + col + 1] = from_f32<TC>(acc[3]);
+        }
+    }
+}
+
+template <typename TC>
+int launch_walk(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw, int ldc,
+                cudaStream_t stream) {
+    static int blocks_cap = 0;
+    auto kern = gemm_skinny_walk_kernel<TC>;
+    const size_t smem = (size_t)16 * (K + XPAD) * sizeof(bf16);
+    if (blocks_cap == 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sms = 148;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)((size_t)16 * (WALK_MAX_K + XPAD) * sizeof(bf16)));
+        if (e != cudaSuccess) return (int)e;
+        blocks_cap = 2 * sms;
+    }
+    const int groups = (N + COLS - 1) / COLS;
+    const int want = (groups + WARPS - 1) / WARPS;
+    const unsigned blocks = (unsigned)(want < blocks_cap ? want : blocks_cap);
+    return sandy_launch(kern, dim3(blocks), dim3(WARPS * 32), smem, stream, (const bf16*)a, (const bf16*)w, (TC*)out, M, N,
+                        K, lda, ldw, ldc);
+}
+
 }  // namespace
 
 // Largest M and K the fused norm takes (the row is held in registers; the normalised rows
@@ -392,6 +495,11 @@ SANDY_API int sandy_gemm_skinny(const void* a, const float* x, int ldx, const vo
         if (!v_cache || !block_table || !token_seq || !positions || out_dtype != SANDY_BF16 || head_dim <= 0 ||
             kv_cols % head_dim != 0 || q_cols + 2 * kv_cols != N || page_size <= 0)
             return SANDY_ERR_ARGUMENT;
+    }
+    if (!fuse && !k_cache && !bias && !residual && act == SANDY_ACT_NONE && M <= 16 && K <= WALK_MAX_K &&
+        (N + COLS - 1) / COLS >= WALK_MIN_GROUPS) {
+        if (out_dtype == SANDY_F32) return launch_walk<float>(a, w, out, M, N, K, lda, ldw, ldc, stream);
+        return launch_walk<bf16>(a, w, out, M, N, K, lda, ldw, ldc, stream);
     }
     if (fuse) return launch<1, true>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
     if (M <= 16) return launch<1, false>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
