@@ -22,8 +22,9 @@
 // Other head sizes are served by the general kernel in attention.cu.
 //
 // Merging the splits.  With up to 8 splits the blocks of one (token, head) pair are launched
-// as one thread-block cluster and merge through distributed shared memory: no scratch, no
-// second kernel (sandy_decode_attention_cluster).  The scratch form with its merge kernel
+// as one thread-block cluster and merge through distributed shared memory: every block writes
+// its partial state into the first block's shared memory, one cluster barrier, the first
+// block merges; no scratch, no second kernel (sandy_decode_attention_cluster).  The scratch form with its merge kernel
 // remains for more splits and for callers that want it (sandy_decode_attention).
 #include <cooperative_groups.h>
 
@@ -75,9 +76,13 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
 
     __shared__ float sm_m[GROUPS], sm_l[GROUPS];
     __shared__ float sm_o[GROUPS][D];
-    __shared__ float cl_o[D], cl_ml[2];        // this block's partial state, read by its cluster
+    __shared__ float cl_all[MAX_CLUSTER_SPLITS][D + 2];   // in the cluster's first block: every split's (output, max, sum)
 
     pdl_launch_dependents();
+    const bool in_cluster = num_splits > 1 && partial_o == nullptr;
+    // A block may write into another block's shared memory only once that block is running: every
+    // block says so here, and waits for the others only when it has its partial state to hand over.
+    if (in_cluster) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     pdl_wait();
     const int split = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -156,6 +161,11 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     __syncthreads();
 
     // merge the groups, one thread per output dimension, fixed order
+    float* first_all = nullptr;                 // cl_all of the cluster's first block
+    if (in_cluster) {
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // everyone arrived long ago
+        first_all = cg::this_cluster().map_shared_rank(&cl_all[0][0], 0);
+    }
     for (int d = threadIdx.x; d < D; d += WARPS * 32) {
         float M = -INFINITY;
 #pragma unroll
@@ -172,11 +182,12 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
         if (num_splits == 1) {
             out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
         } else if (partial_o == nullptr) {
-            // cluster mode: the splits of this (token, head) are the blocks of one cluster
-            cl_o[d] = O;
+            // cluster mode: the splits of this (token, head) are the blocks of one cluster, and each
+            // hands its partial state to the first block's shared memory
+            first_all[split * (D + 2) + d] = O;
             if (d == 0) {
-                cl_ml[0] = M;
-                cl_ml[1] = L;
+                first_all[split * (D + 2) + D] = M;
+                first_all[split * (D + 2) + D + 1] = L;
             }
         } else {
             const size_t slot = ((size_t)t * n_heads + h) * num_splits + split;
@@ -187,29 +198,26 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
             }
         }
     }
-    if (num_splits > 1 && partial_o == nullptr) {
-        // Merge through distributed shared memory: every block leaves its partial state in its
-        // own shared memory, the cluster's first block reads them all (fixed order: split 0, 1, ..)
-        // and writes the result; nobody leaves before that block is done reading.
+    if (in_cluster) {
+        // One barrier makes the partial states visible; the first block then merges them out of
+        // its own shared memory (fixed order: split 0, 1, ..) and nobody else has anything left to do.
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();
         if (cluster.block_rank() == 0) {
             float M = -INFINITY;
-            for (int r = 0; r < num_splits; r++) M = fmaxf(M, cluster.map_shared_rank(cl_ml, r)[0]);
+            for (int r = 0; r < num_splits; r++) M = fmaxf(M, cl_all[r][D]);
             for (int d = threadIdx.x; d < D; d += WARPS * 32) {
                 float L = 0.0f, O = 0.0f;
                 if (M > -INFINITY) {
                     for (int r = 0; r < num_splits; r++) {
-                        const float* rml = cluster.map_shared_rank(cl_ml, r);
-                        const float w = expf(rml[0] - M);
-                        L = fmaf(rml[1], w, L);
-                        O = fmaf(cluster.map_shared_rank(cl_o, r)[d], w, O);
+                        const float w = expf(cl_all[r][D] - M);
+                        L = fmaf(cl_all[r][D + 1], w, L);
+                        O = fmaf(cl_all[r][d], w, O);
                     }
                 }
                 out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
             }
         }
-        cluster.sync();
     }
 }
 
