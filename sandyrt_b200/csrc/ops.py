@@ -516,6 +516,24 @@ GEMM_VARIANTS = (-64, -128, -256, 64, 128, 256, PAIR_TILE + 128, PAIR_TILE + 256
 _gemm_tiles: dict = {}
 
 
+TUNE_LAUNCHES = 8
+
+
+def _time_queued(fn) -> float:
+    """Device milliseconds of TUNE_LAUNCHES calls of fn, run back to back.  A launch costs the host
+    about as long as one of these kernels takes the GPU, so timed naively the host's pace is what is
+    measured; here the GPU is kept busy with a spin kernel while the launches queue up behind it."""
+    fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(600_000)               # ~0.3 ms: the launches below are all queued before it ends
+    e0.record()
+    for _ in range(TUNE_LAUNCHES):
+        fn()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1)
+
+
 def _tuned_tile(launch, a, out, residual, M: int, N: int, K: int, act) -> int:
     key = (-(-M // 128), N, K, ACT_CODES[act], residual is not None, out.dtype, a.device.index)
     hit = _gemm_tiles.get(key)
@@ -525,15 +543,8 @@ def _tuned_tile(launch, a, out, residual, M: int, N: int, K: int, act) -> int:
         return 0
     scratch = torch.empty_like(out)
     best, best_us = 0, float("inf")
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for tile in GEMM_VARIANTS:               # timed without the cache write: the scratch runs must not touch pages
-        launch(tile, scratch, residual, False)
-        e0.record()
-        for _ in range(3):
-            launch(tile, scratch, residual, False)
-        e1.record()
-        e1.synchronize()
-        us = e0.elapsed_time(e1)
+        us = _time_queued(lambda: launch(tile, scratch, residual, False))
         if us < best_us:
             best, best_us = tile, us
     _gemm_tiles[key] = best
@@ -563,18 +574,11 @@ def small_gemm_prefers_tc(a, w, bias, out, *, act=None, residual=None) -> bool:
     if torch.cuda.is_current_stream_capturing() or _recorder is not None:
         return False
     scratch = torch.empty_like(out)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     times = []
     for fn in (lambda: gemm_skinny(a, w, bias, scratch, act=act, residual=residual),
                lambda: gemm_tc(a, w, bias, scratch, act=act, residual=residual, tile_n=64),
                lambda: gemm_tc(a, w, bias, scratch, act=act, residual=residual, tile_n=-64)):
-        fn()
-        e0.record()
-        for _ in range(3):
-            fn()
-        e1.record()
-        e1.synchronize()
-        times.append(e0.elapsed_time(e1))
+        times.append(_time_queued(fn))
     choice = min(times[1:]) < 0.9 * times[0]          # the skinny kernel keeps ties and near-ties
     _small_choice[key] = choice
     if choice:
