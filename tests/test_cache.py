@@ -145,3 +145,18 @@ def test_random_orders_of_requests_never_lose_a_page(seed):
     al.check()
     assert all(p.free_pages == p.num_pages for p in al.pools)
     assert al.free_slots() == 4
+
+
+def test_decode_splits_avoid_clusters_of_six_and_seven():
+    """The splits of a (token, head) pair are one thread-block cluster; sizes 6 and 7 are never asked for."""
+    from sandyrt_b200.csrc.ops import decode_splits
+
+    seen = set()
+    for tokens in range(1, 80):
+        for heads in (1, 2, 12, 16, 25):
+            for max_kv in (64, 128, 512, 1024, 8192):
+                n = decode_splits(tokens, heads, max_kv)
+                assert n >= 1 and n not in (6, 7)
+                assert n <= max(1, max_kv // 64) or n == 5
+                seen.add(n)
+    assert {1, 2, 3, 4, 5, 8} <= seen
