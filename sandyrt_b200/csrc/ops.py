@@ -214,6 +214,9 @@ def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out,
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
 
 
+_FORCED_SPLITS = int(os.environ.get("SANDYRT_DECODE_SPLITS", "0"))      # > 0: this many splits, for comparisons
+
+
 def decode_splits(n_tokens: int, n_heads: int, max_kv: int) -> int:
     """How many blocks share the keys of one (token, head) pair: enough to fill the GPU's 148
     SMs a few times over, but no block with fewer than 64 keys.  It depends on the launch
@@ -228,8 +231,6 @@ def decode_splits(n_tokens: int, n_heads: int, max_kv: int) -> int:
     # against 0.376 ms with 5 (0.383 with 4, 0.420 with 8).
     return 5 if n in (6, 7) else n
 
-
-_FORCED_SPLITS = int(os.environ.get("SANDYRT_DECODE_SPLITS", "0"))      # for comparisons
 
 
 CLUSTER_MAX_SPLITS = 8
