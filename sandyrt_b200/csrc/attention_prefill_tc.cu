@@ -44,8 +44,8 @@
 // threads, with zero fill for keys past the request's last position, so that a poisoned slot
 // never meets a zero of P.  These hold the warps up (each copy instruction of a warp takes
 // about 300 cycles to be taken up, however few are in flight); one TMA copy per page was tried
-// too and is slower still (about 100 ns a copy, sixteen a tile).  Two blocks fit an SM (102 KB
-// of shared memory, 256 columns of tensor memory, 288 threads of 112 registers each).
+// too and is slower still (about 100 ns a copy, sixteen a tile).  Two blocks fit an SM (106 KB
+// of shared memory, 256 columns of tensor memory, 288 threads of 96 registers each).
 //
 // Like every attention kernel here it reads all keys from the cache (the step's own keys are
 // appended first): query i of a portion sits at position kv_before + i and sees keys
