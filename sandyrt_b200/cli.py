@@ -3,7 +3,6 @@
     python -m sandyrt_b200 generate --model DIR --prompt-ids 1,2,3 [options]
     python -m sandyrt_b200 random-model --config config.json --out DIR [--seed S] [--dtype bfloat16]
     python -m sandyrt_b200 replay --model DIR --dtype float32 --out DIR --max-tokens N < steps.jsonl
-    python -m sandyrt_b200 program-timeline --model DIR [--batch 8] [--context 300]
 
 Option names follow the reference's worker where it has them (src/server/SandyWorkerMain.cpp:30-39:
 --model, --prefill-chunk-tokens, --eos-token-id, --max-context-tokens, --profile, --debug) and
@@ -73,50 +72,6 @@ def cmd_replay(a) -> int:
     return run(a.model, a.dtype, a.out, a.max_tokens, sys.stdin, page_size=a.page_size)
 
 
-def cmd_program_timeline(a) -> int:
-    """Run decode steps of `batch` requests at about `context` tokens as a decode program and print
-    where block 0 spent the time of one launch, operation by operation."""
-    import numpy as np
-    import torch
-
-    from .engine.step import Engine, StepEntry
-    from .models.model import load_model
-
-    model = load_model(a.model, device="cuda:0", dtype=torch.bfloat16)
-    eng = Engine(model, max_tokens=a.batch * (a.context + 64) + 1024, max_requests=max(a.batch, 1),
-                 max_step_tokens=max(2048, a.context), use_cuda_graphs=False, use_decode_programs=True)
-    rng = np.random.default_rng(0)
-    vocab = model.spec.vocab_size
-    for i in range(a.batch):
-        eng.step([StepEntry(i, rng.integers(0, vocab, size=a.context).tolist(), [])])
-    for _ in range(4):
-        eng.step([StepEntry(i, [int(rng.integers(0, vocab))], [0]) for i in range(a.batch)])
-    hits = [h for h in eng._programs.values() if h is not None]
-    if not hits:
-        print("this model's decode step cannot be recorded as a program", file=sys.stderr)
-        return 1
-    prog = hits[-1][0]
-    tl = torch.zeros(3 * prog.n_ops + 1, dtype=torch.int64, device="cuda:0")
-    for _ in range(3):      # the last run is the one read: same inputs, caches warm
-        prog.run(tl)
-        torch.cuda.synchronize()
-    eng.check_status()
-    t = tl.cpu().numpy().astype(np.int64)
-    names = {0: "embed", 1: "norm", 2: "gemm", 3: "attn"}
-    print(f"{prog.n_ops} operations, {(t[-1] - t[0]) / 1e3:.1f} us on block 0's clock")
-    print(" op kind    total   staged    work  barrier   (us; staged: inputs in shared memory / first keys asked for)")
-    total = {}
-    for i in range(prog.n_ops):
-        s0, m0, m1, end = t[3 * i], t[1 + 3 * i], t[2 + 3 * i], t[3 + 3 * i]
-        staged = (m0 - s0) / 1e3 if m0 else 0.0
-        work = (m1 - (m0 if m0 else s0)) / 1e3
-        kind = names[prog.kinds[i]]
-        total[kind] = total.get(kind, 0.0) + (end - s0) / 1e3
-        print(f"{i:3d} {kind:5s} {(end - s0) / 1e3:7.2f} {staged:8.2f} {work:7.2f} {(end - m1) / 1e3:8.2f}")
-    print("by kind:", ", ".join(f"{k} {v:.1f} us" for k, v in total.items()))
-    return 0
-
-
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="sandyrt_b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -157,12 +112,6 @@ def main(argv: Optional[List[str]] = None) -> int:
     t.add_argument("--max-tokens", type=int, required=True)
     t.add_argument("--page-size", type=int, default=16)
     t.set_defaults(fn=cmd_replay)
-
-    pt = sub.add_parser("program-timeline", help="time a decode step run as one resident kernel, operation by operation")
-    pt.add_argument("--model", required=True)
-    pt.add_argument("--batch", type=int, default=8)
-    pt.add_argument("--context", type=int, default=300)
-    pt.set_defaults(fn=cmd_program_timeline)
 
     a = ap.parse_args(argv)
     return a.fn(a)

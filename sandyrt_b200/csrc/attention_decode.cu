@@ -414,8 +414,20 @@ SANDY_API int sandy_decode_attention_static(const void* q, int ld_q, const void*
                                             int* status, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (n_tokens < 0 || n_heads <= 0 || head_dim <= 0 || num_splits < 1) return SANDY_ERR_ARGUMENT;
-    const long long need = sandy_decode_attention_scratch_floats(n_tokens, n_heads, head_dim, num_splits);
-    if (need > (long long)SANDY_DECODE_STATIC_SCRATCH_FLOATS) return SANDY_ERR_STATIC_SCRATCH;
+    // Bound every factor before multiplying, so that the product below cannot wrap around and
+    // slip under the capacity: no factor alone may exceed what the whole array holds.
+    const long long cap = (long long)SANDY_DECODE_STATIC_SCRATCH_FLOATS;
+    if (head_dim > 256) return SANDY_ERR_UNSUPPORTED;
+    if (n_tokens > cap || n_heads > cap || num_splits > cap) return SANDY_ERR_STATIC_SCRATCH;
+    long long need = 0;
+    if (num_splits > 1) {
+        need = (long long)n_tokens * n_heads;                 // <= 2^40
+        if (need > cap) return SANDY_ERR_STATIC_SCRATCH;
+        need *= num_splits;                                   // <= 2^40
+        if (need > cap) return SANDY_ERR_STATIC_SCRATCH;
+        need *= head_dim + 2;                                 // <= 2^29
+    }
+    if (need > cap) return SANDY_ERR_STATIC_SCRATCH;
     int error = SANDY_OK;
     float* scratch = static_scratch_address(&error);     // first call on a device: the one-time look-up
     if (scratch == nullptr) return error;

@@ -333,7 +333,7 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
     // Many blocks: a short ring each, so that more blocks share an SM (measured on 64 x 12 pairs of
     // 384 keys: 18.8 us with 16 KB, 25.6 us with 32 KB); few blocks: a longer ring each.
     const long long blocks = (long long)num_splits * n_heads * n_tokens;
-    const int ring = g_ring_bytes > 0 ? g_ring_bytes : (blocks >= 3 * 148 ? 16 * 1024 : 32 * 1024);
+    const int ring = g_ring_bytes > 0 ? g_ring_bytes : (blocks >= 3LL * sandy_sm_count() ? 16 * 1024 : 32 * 1024);
     int n_stages = (int)(ring / stage_bytes);
     // A multiple of WARPS, so that a stage always serves the same warp: a warp that skipped a
     // phase of a stage's barrier could not tell the phases apart by their parity.

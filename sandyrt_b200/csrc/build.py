@@ -42,7 +42,6 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention": [],
     "attention_decode": [],
     "attention_decode_bulk": [],
-    "decode_program": [],
     "attention_prefill": [],
     "attention_prefill_tc": [],
     "sampling": [],

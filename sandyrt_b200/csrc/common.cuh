@@ -76,6 +76,19 @@ static inline int sandy_launch_status() {
     return (int)cudaGetLastError();
 }
 
+// Streaming multiprocessors of the current device, asked once per library (grids and split
+// counts are sized by it; no kernel assumes a particular GPU's count).
+static inline int sandy_sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess)
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms = n > 0 ? n : 1;
+    }
+    return sms;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------
 // A decode step is a chain of ~70 short kernels, each only a few microseconds long, so what
 // a kernel costs is mostly getting started: launch latency and the first trip to memory.

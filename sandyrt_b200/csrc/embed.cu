@@ -52,3 +52,25 @@ SANDY_API int sandy_embed_pos(const int* ids, const int* pos, const void* wte, c
 #undef LAUNCH
     return SANDY_ERR_UNSUPPORTED;
 }
+
+// ---- small device utilities the host side uses -------------------------------------------------
+SANDY_API int sandy_device_sm_count() { return sandy_sm_count(); }
+
+// Keeps the stream busy for about `nanoseconds` (at most 10 ms) and does nothing else.  Timing
+// loops queue their launches behind it, so that the GPU runs them back to back instead of at
+// the pace the host issues them.
+__global__ void spin_kernel(unsigned long long nanoseconds) {
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    do {
+        __nanosleep(200);
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    } while (t - t0 < nanoseconds);
+}
+
+SANDY_API int sandy_spin(long long nanoseconds, cudaStream_t stream) {
+    if (nanoseconds <= 0) return SANDY_OK;
+    if (nanoseconds > 10000000LL) nanoseconds = 10000000LL;
+    spin_kernel<<<1, 1, 0, stream>>>((unsigned long long)nanoseconds);
+    return sandy_launch_status();
+}

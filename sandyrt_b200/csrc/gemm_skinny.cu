@@ -436,9 +436,7 @@ int launch_walk(const void* a, const void* w, void* out, int M, int N, int K, in
     auto kern = gemm_skinny_walk_kernel<TC>;
     const size_t smem = (size_t)16 * (K + XPAD) * sizeof(bf16);
     if (blocks_cap == 0) {
-        int dev = 0, sms = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            sms = 148;
+        const int sms = sandy_sm_count();
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)((size_t)16 * (WALK_MAX_K + XPAD) * sizeof(bf16)));
         if (e != cudaSuccess) return (int)e;

@@ -339,13 +339,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs& ep,
 //   persistent:                                rounds(tiles / SMs) x tile bytes / rate + one epilogue
 // The constants come from `python -m sandyrt_b200.csrc.microbench gemm` (2048 rows, GPT-2 small).
 int choose_tile(int M, int N, int K) {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            n = 148;
-        sms = n > 0 ? n : 148;
-    }
+    const int sms = sandy_sm_count();
     const double rate = 70e3, all_rate = 9e6;        // bytes per microsecond: one SM, all SMs
     const int k_tiles = (K + BK - 1) / BK, m_tiles = (M + BM - 1) / BM;
     double best = 1e30;

@@ -49,17 +49,6 @@ def _stream():
 # Number of kernel launches issued through this module (benchmarks report it).
 LAUNCHES = 0
 
-# While a decode program is being recorded (program.recording) the functions a decode step uses
-# append a record to it instead of launching; every other function refuses.
-_recorder = None
-
-
-def _no_record(what: str) -> None:
-    if _recorder is not None:
-        from .program import NotRecordable
-        raise NotRecordable(what)
-
-
 def _check(code: int, what: str) -> None:
     global LAUNCHES
     LAUNCHES += 1
@@ -95,8 +84,6 @@ def embed_positions(ids, positions, wte, wpe, out, status=None) -> None:
             raise KernelError("position table must match the token table in dtype and width")
     if wte.shape[1] != width or not (wte.is_contiguous() and out.is_contiguous()):
         raise KernelError("embed_positions: tables and output must be contiguous and of one width")
-    if _recorder is not None:
-        return _recorder.embed(ids, positions, wte, wpe, out, status)
     lib = load_library("embed")
     code = lib.sandy_embed_pos(_p(ids), _p(positions), _p(wte), _p(wpe), _p(out),
                                ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(wte.shape[0]),
@@ -118,8 +105,6 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
         raise KernelError("layernorm: x and out disagree")
     if not (x.is_contiguous() and out.is_contiguous()) or out.shape[-1] != width or gamma.numel() != width:
         raise KernelError("layernorm: contiguous [rows, width] tensors expected")
-    if _recorder is not None:
-        return _recorder.norm(x, gamma, beta, eps, out, rows)
     lib = load_library("norm")
     code = lib.sandy_layernorm(_p(x), _p(gamma), _p(beta), _p(out), _p(rows), ctypes.c_int(n_rows),
                                ctypes.c_int(width), ctypes.c_float(eps), ctypes.c_int(_dt(x)),
@@ -129,7 +114,6 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
 
 def gemm_simt(a, w, bias, out, *, w_out_in: bool, act=None, residual=None) -> None:
     """out = act(a @ W + bias) + residual on the 32-bit pipes.  W is [K,N], or [N,K] with w_out_in."""
-    _no_record("a float32 product")
     _cuda(a, w, bias, out, residual)
     M, K = a.shape
     N = out.shape[1]
@@ -168,7 +152,6 @@ def _cache_args(k_cache, v_cache):
 
 def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions) -> None:
     """Write the step's keys/values ([T, Hkv*D] views, one row stride) into their pages."""
-    _no_record("a separate key/value write")
     _cuda(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = k_src.shape[0]
@@ -188,7 +171,6 @@ def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
 def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *,
                     n_heads: int, scale: float, window: int = 0) -> None:
     """Causal attention of every token of the step over its request's pages (general kernel)."""
-    _no_record("the general attention kernel")
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -217,13 +199,31 @@ _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16,
 _FORCED_SPLITS = int(os.environ.get("SANDYRT_DECODE_SPLITS", "0"))      # > 0: this many splits, for comparisons
 
 
-def decode_splits(n_tokens: int, n_heads: int, max_kv: int) -> int:
-    """How many blocks share the keys of one (token, head) pair: enough to fill the GPU's 148
+_SM_COUNT = 0
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (asked once)."""
+    global _SM_COUNT
+    if _SM_COUNT == 0:
+        _SM_COUNT = int(load_library("embed").sandy_device_sm_count())
+    return _SM_COUNT
+
+
+def spin(nanoseconds: int) -> None:
+    """Keep the current stream busy for about this long (timing loops queue their launches behind it)."""
+    code = load_library("embed").sandy_spin(ctypes.c_longlong(int(nanoseconds)), _stream())
+    if code:
+        raise KernelError(f"spin: CUDA error {code}")
+
+
+def decode_splits(n_tokens: int, n_heads: int, max_kv: int, sms: Optional[int] = None) -> int:
+    """How many blocks share the keys of one (token, head) pair: enough to fill the GPU's
     SMs a few times over, but no block with fewer than 64 keys.  It depends on the launch
     shape only (not on the requests' exact lengths), so a recorded graph stays valid."""
     if _FORCED_SPLITS:
         return _FORCED_SPLITS
-    want = -(-4 * 148 // max(1, n_tokens * n_heads))
+    want = -(-4 * (sms or sm_count()) // max(1, n_tokens * n_heads))
     cap = max(1, max_kv // 64)
     n = max(1, min(want, cap, 32))
     # The splits of a pair are one thread-block cluster.  Clusters of 6 and 7 blocks pack badly into
@@ -251,7 +251,6 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
     kernel; otherwise they go through `scratch` and a merge kernel.  `bulk` (at most 8 splits)
     runs the variant that streams whole pages into shared memory with bulk copies, which is
     the faster one when there are hundreds of (token, head) pairs."""
-    _no_record("a decode attention kernel called by name")
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, scratch)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -315,7 +314,6 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
     q_start: int32 [S+1] first new token of each request; kv_before: int32 [S].
     tc: True asks for the tcgen05 kernel (heads of 64), False for the mma.sync kernel, None
     picks the tcgen05 kernel where it takes the shape."""
-    _no_record("attention of prompt portions")
     _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     if q.dtype != torch.bfloat16 or d % 16 != 0 or d > 128:
@@ -353,14 +351,6 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
 def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale: float, window: int = 0) -> None:
     """Attention of a step's tokens over the cache: picks the kernel for the step's shape."""
     d = k_cache.shape[3]
-    if _recorder is not None:
-        if ctx.max_q_len != 1:
-            _no_record("attention of prompt portions")
-        hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
-        _i32(block_table, "block_table")
-        return _recorder.attention(q, k_cache, v_cache, page_stride, num_pages, block_table, ctx.token_seq,
-                                   ctx.positions, out, n_heads=n_heads, n_kv_heads=hkv, head_dim=d, page_size=ps,
-                                   scale=scale, window=window)
     if ctx.max_q_len > 1 and q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 128:
         prefill_attention(q, k_cache, v_cache, block_table, ctx.q_start, ctx.kv_before, out, n_heads=n_heads,
                           max_q_len=ctx.max_q_len, scale=scale, window=window)
@@ -384,7 +374,6 @@ def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, unif
     feedback: (token_ids, logit_rows, positions, burst_tokens, row_step) int32 device tensors: the
     drawn token also replaces the row's input token, its position moves on, and the token is
     recorded in burst_tokens[row_step[r], r]; `uniform` then holds [steps, rows] numbers."""
-    _no_record("sampling")
     _cuda(logits, out_tokens, temperature, top_k, top_p, uniform, status)
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 with unit inner stride")
@@ -433,12 +422,10 @@ def check_kernel_status(device) -> None:
     code = int(t.item())
     if code:
         t.zero_()
-        from . import program
-        program.reset_sync()
         raise KernelError(f"a kernel reported a fault (status {code}: bits 0-2 a barrier wait ran out in the "
                           "tensor-core product, bit 3 a key/value write and bit 4 a key read had no page behind "
-                          "it, bits 5-6 a wait ran out in the bulk decode attention, bit 7 in the decode "
-                          "program, bit 8 in the tcgen05 prefill attention); the step's output is not valid")
+                          "it, bits 5-6 a wait ran out in the bulk decode attention, "
+                          "bit 8 in the tcgen05 prefill attention); the step's output is not valid")
 
 
 def tensor_core_gemm_supported(K: int, N: int) -> bool:
@@ -451,7 +438,6 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0, kv=Non
     """out = act(a @ w.T + bias) + residual on the tcgen05 tensor cores.
     a: bfloat16 [M, K]; w: bfloat16 [N, K]; out: bfloat16 or float32 [M, N].  With `kv` (a
     KVTarget) the key and value columns of the product also go into the cache pages."""
-    _no_record("a tensor-memory product")
     _cuda(a, w, bias, out, residual)
     M, K = a.shape
     N = w.shape[0]
@@ -506,7 +492,7 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0, kv=Non
 
 # Which of the tcgen05 variants (three tile widths, one tile per CTA or persistent; two CTAs on a
 # 256-row tile, two widths) is fastest
-# depends on how the tiles of a product fall on the 148 SMs, and a model of it was off by 20 % on
+# depends on how the tiles of a product fall on the SMs, and a model of it was off by 20 % on
 # half the shapes tried.  So the first product of a shape (rows in steps of 128) with at least
 # this many rows times each variant on a scratch output and remembers the winner.  All variants
 # add the k-steps of an output element in the same order, so the choice never changes a result.
@@ -526,7 +512,7 @@ def _time_queued(fn) -> float:
     measured; here the GPU is kept busy with a spin kernel while the launches queue up behind it."""
     fn()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda._sleep(600_000)               # ~0.3 ms: the launches below are all queued before it ends
+    spin(300_000)                            # 0.3 ms: the launches below are all queued before it ends
     e0.record()
     for _ in range(TUNE_LAUNCHES):
         fn()
@@ -556,36 +542,18 @@ SKINNY_NORM_MAX_ROWS = 16
 SKINNY_NORM_MAX_K = 2048
 
 # Between 17 and 64 rows neither kernel always wins (measured at 64 rows on GPT-2 small: the
-# up-projection 5.9 us on tcgen05 against 10.7 us skinny, the out-projection 6.1 against 4.2), so
-# a product of that size with nothing fused into it is timed both ways on first sight, like the
-# tcgen05 variants above.
-_small_choice: dict = {}
+# up-projection, 3,072 columns, 5.9 us on tcgen05 against 10.7 us skinny; the out-projection, 768
+# columns, 6.1 against 4.2: a 128 x 64 tile per CTA leaves most SMs idle when there are few
+# columns).  The two kernels add in different orders, so the choice is a fixed rule of the shape
+# and never a timing: the same batch gives the same bfloat16 tokens in every process.
+SMALL_TC_MIN_ROWS = 33
+SMALL_TC_MIN_COLS = 2048
 
 
-def small_gemm_prefers_tc(a, w, bias, out, *, act=None, residual=None) -> bool:
-    """Whether a 17..64-row product should go to the tcgen05 kernel instead of the skinny one.
-    Times both once per (rows in steps of 16, N, K, epilogue) on a scratch output; while a CUDA
-    graph is being captured an unknown shape stays with the skinny kernel."""
-    M, K = a.shape
-    N = w.shape[0]
-    key = (-(-M // 16), N, K, ACT_CODES[act], residual is not None, out.dtype, a.device.index)
-    hit = _small_choice.get(key)
-    if hit is not None:
-        return hit
-    if torch.cuda.is_current_stream_capturing() or _recorder is not None:
-        return False
-    scratch = torch.empty_like(out)
-    times = []
-    for fn in (lambda: gemm_skinny(a, w, bias, scratch, act=act, residual=residual),
-               lambda: gemm_tc(a, w, bias, scratch, act=act, residual=residual, tile_n=64),
-               lambda: gemm_tc(a, w, bias, scratch, act=act, residual=residual, tile_n=-64)):
-        times.append(_time_queued(fn))
-    choice = min(times[1:]) < 0.9 * times[0]          # the skinny kernel keeps ties and near-ties
-    _small_choice[key] = choice
-    if choice:
-        _gemm_tiles[(-(-M // 128), N, K, ACT_CODES[act], residual is not None, out.dtype, a.device.index)] = \
-            64 if times[1] <= times[2] else -64
-    return choice
+def small_gemm_prefers_tc(M: int, N: int, K: int) -> bool:
+    """Whether a 17..64-row product with nothing fused into it goes to the tcgen05 kernel (one
+    128 x 64 tile per CTA) instead of the skinny one."""
+    return M >= SMALL_TC_MIN_ROWS and N >= SMALL_TC_MIN_COLS and tensor_core_gemm_supported(K, N)
 
 
 def skinny_norm_fusable(lazy, K: int) -> bool:
@@ -645,10 +613,6 @@ def gemm_skinny(a, w, bias, out, *, act=None, residual=None, norm=None, kv=None)
         if kc.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kv_cols != hkv * head_dim \
                 or q_cols + 2 * kv_cols != N or kv.head_dim != head_dim:
             raise KernelError("gemm_skinny: the key/value target does not match the product")
-    if _recorder is not None:
-        kvrec = None if kv is None else (kc, vc, table, tseq, tpos, page_stride, q_cols, kv_cols, head_dim,
-                                         page_size, num_pages)
-        return _recorder.gemm(a, x, gamma, beta, eps, w, bias, residual, out, ACT_CODES[act], _dt(out), kvrec)
     lib = load_library("gemm_skinny")
     code = lib.sandy_gemm_skinny(
         _p(a), _p(x), ctypes.c_int(0 if x is None else x.stride(0)), _p(gamma), _p(beta), ctypes.c_float(eps),

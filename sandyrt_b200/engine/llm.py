@@ -84,7 +84,7 @@ class LLM:
                              max_step_tokens=max_step_tokens, use_cuda_graphs=use_cuda_graphs)
         self.scheduler = Scheduler(self.engine.cache.alloc, max_step_tokens=max_step_tokens,
                                    prefill_chunk=prefill_chunk_tokens, max_live=max_live,
-                                   max_positions=limit)
+                                   max_positions=limit, admit=self.engine.admit)
         self.eos_token_ids = frozenset(int(t) for t in (eos_token_ids or ()))
         self.max_burst = max(1, min(int(max_burst), MAX_BURST)) if self.engine.use_cuda_graphs else 1
         self.decode_steps_run = 0
@@ -97,7 +97,6 @@ class LLM:
         self._requests: Dict[Hashable, Request] = {}
         self._seeds: Dict[Hashable, int] = {}
         self._next_id = 0
-        self._token_host = torch.empty(max(max_live, 1), dtype=torch.int32, pin_memory=True)
 
     # ---- request interface ----------------------------------------------------------------
     def add_request(self, prompt_ids: Sequence[int], *, max_tokens: int = 16,
@@ -172,14 +171,13 @@ class LLM:
         order.  A request that finishes part of the way (or was finished or aborted while the
         burst ran) keeps only the tokens up to its finish; what the device computed for it after
         that is dropped."""
-        tokens = self.engine.burst_tokens(handle)
+        tokens = self.engine.burst_tokens(handle)       # raises if a kernel of the burst reported a fault
         n = handle.n
         self.decode_steps_run += n
         now = time.perf_counter()
         got: List[Tuple[Request, int]] = []
         alive = [i for i, r in enumerate(reqs) if r.state is RequestState.RUNNING]
         if any(int(tokens[j, i]) < 0 for j in range(n) for i in alive):
-            self.engine.check_status()
             raise ValueError("sampling logits must not contain NaN")         # Sampler.cpp:64-67
         for j in range(n):
             if not alive:
@@ -247,19 +245,12 @@ class LLM:
             sp = r.sampling
             rows.append(SampleRow(0.0 if sp.greedy else sp.temperature, sp.top_k, sp.top_p,
                                   0.0 if sp.greedy else uniform_for(self._seeds[r.rid], len(r.output))))
-        self.engine.step(entries, sampling=rows, reserved=True)
+        self.engine.step(entries, sampling=rows)
         sampled: Dict[Hashable, int] = {}
         if sampled_reqs:
             n = len(sampled_reqs)
-            tokens = self.engine.sampled_tokens(n)
-            if self._token_host.numel() < n:
-                self._token_host = torch.empty(n, dtype=torch.int32, pin_memory=True)
-            self._token_host[:n].copy_(tokens, non_blocking=True)
-            self.engine.d2h_bytes_total += 4 * n
-            torch.cuda.current_stream().synchronize()
-            host = self._token_host[:n].tolist()
+            host = self.engine.read_sampled(n)          # raises if a kernel of the step reported a fault
             if any(t < 0 for t in host):
-                self.engine.check_status()
                 raise ValueError("sampling logits must not contain NaN")     # Sampler.cpp:64-67
             sampled = {r.rid: t for r, t in zip(sampled_reqs, host)}
         now = time.perf_counter()

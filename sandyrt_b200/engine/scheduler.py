@@ -96,10 +96,14 @@ class StepPlan:
 
 class Scheduler:
     def __init__(self, alloc: BlockAllocator, *, max_step_tokens: int = 2048, prefill_chunk: int = 2048,
-                 max_live: int = 64, max_positions: Optional[int] = None):
+                 max_live: int = 64, max_positions: Optional[int] = None, admit=None):
+        """admit: how a request takes its state slot (default: the allocator's own `admit`).  The
+        entry point passes the cache manager's, which also zeroes the slot's fixed-size state on
+        the device, so that a request never starts from the state of the slot's last holder."""
         if max_step_tokens <= 0 or prefill_chunk <= 0 or max_live <= 0:
             raise ValueError("token budget, chunk size and request limit must be positive")
         self.alloc = alloc
+        self._admit = admit if admit is not None else alloc.admit
         self.max_step_tokens = max_step_tokens
         self.prefill_chunk = prefill_chunk
         self.max_live = max_live
@@ -217,7 +221,7 @@ class Scheduler:
             if any(n > self.alloc.free_pages(g) for g, n in enumerate(needed)):
                 break
             self.waiting.popleft()
-            self.alloc.admit(req.rid)
+            self._admit(req.rid)
             self.alloc.reserve(req.rid, first)
             req.state = RequestState.RUNNING
             req.admitted_at = self._admissions

@@ -36,7 +36,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pages import FREED, OutOfPages
-from ..csrc import ops, program
+from ..csrc import ops
 from ..models.model import Model
 from ..parts.base import StepContext, Workspace
 
@@ -114,7 +114,7 @@ class BurstHandle:
     """A burst of decode steps queued on the device (Engine.decode_burst_async)."""
     n: int                       # steps
     S: int                       # requests
-    host: torch.Tensor           # pinned int32 buffer the tokens are copied to
+    host: torch.Tensor           # pinned int32 buffer the tokens are copied to; the two status words follow them
     done: torch.cuda.Event       # recorded behind that copy
 
 
@@ -122,8 +122,7 @@ class Engine:
     """A bound model, its cache and the step function over them."""
 
     def __init__(self, model: Model, *, max_tokens: int, page_size: int = 16, max_requests: int = 64,
-                 max_step_tokens: int = 2048, use_cuda_graphs: bool = True,
-                 use_decode_programs: Optional[bool] = None):
+                 max_step_tokens: int = 2048, use_cuda_graphs: bool = True):
         if model.device is None:
             raise StepError("the model has no weights bound")
         if model.device.type != "cuda":
@@ -143,26 +142,19 @@ class Engine:
         self._sampled = torch.zeros(max(max_requests, 1), dtype=torch.int32, device=self.device)
         self._burst_tokens = torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, device=self.device)
         # two pinned buffers: the tokens of one burst are read while the next one runs
-        self._burst_hosts = [torch.zeros(MAX_BURST * max(max_requests, 1), dtype=torch.int32, pin_memory=True)
+        self._burst_hosts = [torch.zeros(MAX_BURST * max(max_requests, 1) + 2, dtype=torch.int32, pin_memory=True)
                              for _ in range(2)]
+        self._token_host = torch.zeros(max(max_requests, 1) + 2, dtype=torch.int32, pin_memory=True)
         self._burst_turn = 0
         self._burst_flip = 0
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
-        # Optional: decode steps of up to 16 tokens as ONE resident kernel that interprets the step's
-        # operations (csrc/program.py).  Off unless asked for (argument, or SANDYRT_DECODE_PROGRAM=1):
-        # measured on GPT-2 small it is slower than the chain of kernels under a CUDA graph (8
-        # requests: 0.66 ms against 0.40 ms a step), see decode_program.cu.
-        if use_decode_programs is None:
-            use_decode_programs = os.environ.get("SANDYRT_DECODE_PROGRAM", "0") == "1"
-        self.use_decode_programs = bool(use_decode_programs) and self.dtype == torch.bfloat16 and model.graph_safe
-        self._programs: Dict[Tuple, Optional[Tuple]] = {}
-        self.program_runs = 0
         self._graphs: Dict[Tuple, Tuple] = {}
         self._seen: Dict[Tuple, int] = {}
         self._table_rows: Dict[Tuple[Hashable, int], Tuple[int, np.ndarray]] = {}
         self.steps_run = 0
         self.graph_replays = 0
         self.stale_graphs = 0
+        self.burst_graphs_recorded = 0   # whole bursts recorded as one graph so far
         self.last_h2d_bytes = 0
         self.h2d_bytes_total = 0         # bytes of step arrays copied to the device so far
         self.d2h_bytes_total = 0         # bytes of drawn tokens copied back so far (bursts; the entry point adds its own)
@@ -364,36 +356,9 @@ class Engine:
         return _Prepared(ctx, sample_dev, key, burst)
 
     # ---- running it ------------------------------------------------------------------------
-    def _program_for(self, p: _Prepared):
-        """The recorded program of this step's shape, recording it on first sight; None if the
-        step is not a small decode step or the model cannot be recorded.  Never called while a
-        CUDA graph is being captured (recording allocates and copies)."""
+    def _run(self, p: _Prepared) -> torch.Tensor:
         ctx = p.ctx
-        if not self.use_decode_programs or p.key is None or ctx.max_q_len != 1 \
-                or ctx.n_tokens > program.limits()["max_rows"]:
-            return None
-        hit = self._programs.get(p.key, False)
-        if hit is not False and (hit is None or hit[2] == self.workspace.version):
-            return hit
-        try:
-            with program.recording(self.device, ops.kernel_status(self.device)) as rec:
-                logits = self.model.forward(ctx, status=self._status)
-            hit = (rec.finish(), logits, self.workspace.version)
-        except program.NotRecordable:
-            hit = None
-        while len(self._programs) >= MAX_GRAPHS:
-            del self._programs[next(iter(self._programs))]
-        self._programs[p.key] = hit
-        return hit
-
-    def _run(self, p: _Prepared, prog=None) -> torch.Tensor:
-        ctx = p.ctx
-        if prog is not None:
-            prog[0].run()
-            logits = prog[1]
-            self.program_runs += 1
-        else:
-            logits = self.model.forward(ctx, status=self._status)
+        logits = self.model.forward(ctx, status=self._status)
         R = ctx.logit_rows.numel()
         if p.sample is not None and R:
             f = p.sample.view(torch.float32)
@@ -423,19 +388,21 @@ class Engine:
         self._seen[key] = seen + 1
         return None, seen >= record_at
 
-    def _record(self, key: Tuple, p: _Prepared, prog, times: int):
+    def _record(self, key: Tuple, p: _Prepared, times: int):
         before = ops.LAUNCHES
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for _ in range(times):
-                logits = self._run(p, prog)
+                logits = self._run(p)
         n_launch = (ops.LAUNCHES - before) // times
         while len(self._graphs) >= MAX_GRAPHS:          # the oldest recording makes room
             del self._graphs[next(iter(self._graphs))]
             self._seen.clear()
         hit = (graph, logits, n_launch, self.workspace.version)
         self._graphs[key] = hit
+        if times > 1:
+            self.burst_graphs_recorded += 1
         return hit
 
     def _execute(self, p: _Prepared, times: int = 1) -> torch.Tensor:
@@ -448,13 +415,12 @@ class Engine:
         shape pay for it; kept in two copies used in turn (the key carries the turn), because a
         graph launched again while it still runs makes the host wait for it, and the host has the
         next burst to prepare."""
-        prog = self._program_for(p)
         before = ops.LAUNCHES
         key = p.key
         if key is None or not self.use_cuda_graphs:
             logits = None
             for _ in range(times):
-                logits = self._run(p, prog)
+                logits = self._run(p)
             self.last_launches = (ops.LAUNCHES - before) // times
             return logits
         step_key = key
@@ -462,7 +428,7 @@ class Engine:
             step_key = key[:6] + (1, 0) + key[8:]           # any burst length, either turn
             hit, record = self._graph_for(key, record_at=2)
             if hit is None and record:
-                hit = self._record(key, p, prog, times)
+                hit = self._record(key, p, times)
             if hit is not None:
                 hit[0].replay()
                 self.graph_replays += times
@@ -470,7 +436,7 @@ class Engine:
                 return hit[1]
         hit, record = self._graph_for(step_key, record_at=1)
         if hit is None and record:
-            hit = self._record(step_key, p, prog, 1)
+            hit = self._record(step_key, p, 1)
         if hit is not None:
             for _ in range(times):
                 hit[0].replay()
@@ -479,12 +445,11 @@ class Engine:
             return hit[1]
         logits = None
         for _ in range(times):
-            logits = self._run(p, prog)
+            logits = self._run(p)
         self.last_launches = (ops.LAUNCHES - before) // times
         return logits
 
-    def step(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]] = None,
-             reserved: bool = False) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], sampling: Optional[Sequence[SampleRow]] = None) -> torch.Tensor:
         """Run one step; returns float32 logits [wanted, vocab] on the device.  The tensor is
         workspace memory: the next step overwrites it.  With `sampling` (one SampleRow per
         wanted place) the drawn tokens are in `self.sampled_tokens(n)` afterwards."""
@@ -534,7 +499,8 @@ class Engine:
         host = self._burst_hosts[self._burst_turn]
         self._burst_turn ^= 1
         host[:n * S].copy_(self._burst_tokens[:n * S], non_blocking=True)
-        self.d2h_bytes_total += 4 * n * S
+        self._copy_status(host, n * S)
+        self.d2h_bytes_total += 4 * n * S + 8
         done = torch.cuda.Event()
         done.record()
         self.steps_run += n
@@ -543,11 +509,36 @@ class Engine:
     def burst_tokens(self, handle: "BurstHandle") -> np.ndarray:
         """Wait for a burst queued by decode_burst_async; its tokens, int32 [n, requests]."""
         handle.done.synchronize()
+        self._raise_on_status(handle.host, handle.n * handle.S)
         return handle.host[:handle.n * handle.S].numpy().reshape(handle.n, handle.S).copy()
 
     def commit(self, rid: Hashable, new_len: int) -> None:
         """Advance a request's length after a burst (see decode_burst)."""
         self.cache.alloc.commit(rid, new_len)
+
+    def _copy_status(self, host: torch.Tensor, at: int) -> None:
+        """Queue copies of the two status words (bad input, kernel faults) to host[at], host[at + 1],
+        behind whatever the stream holds: they travel with the drawn tokens, at no extra wait."""
+        host[at:at + 1].copy_(self._status, non_blocking=True)
+        host[at + 1:at + 2].copy_(ops.kernel_status(self.device), non_blocking=True)
+
+    def _raise_on_status(self, host: torch.Tensor, at: int) -> None:
+        bad_input, fault = int(host[at]), int(host[at + 1])
+        if bad_input or fault:
+            self.check_status()          # clears the words and raises with their meaning
+
+    def read_sampled(self, n: int) -> List[int]:
+        """The tokens drawn by the last step with `sampling`, on the host.  The step's status words
+        come back in the same wait; a non-zero one raises (the tokens are not valid then)."""
+        if self._token_host.numel() < n + 2:
+            self._token_host = torch.zeros(n + 2, dtype=torch.int32, pin_memory=True)
+        host = self._token_host
+        host[:n].copy_(self._sampled[:n], non_blocking=True)
+        self._copy_status(host, n)
+        self.d2h_bytes_total += 4 * n + 8
+        torch.cuda.current_stream().synchronize()
+        self._raise_on_status(host, n)
+        return host[:n].tolist()
 
     def sampled_tokens(self, n: int) -> torch.Tensor:
         """The tokens drawn by the last step with `sampling` (int32 [n] on the device)."""

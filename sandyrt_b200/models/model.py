@@ -20,7 +20,6 @@ import torch
 
 from ..config.base import ModelConfig, load_config
 from ..parts.base import Block, LayerCallCtx, StepContext
-from ..parts.embedding import OutputHead, TokenEmbedding
 from ..registry import get_architecture, get_part
 from ..weights.loader import TensorRequest, load_weights
 from .spec import LayerSpec, ModelSpec, PartSpec
@@ -40,11 +39,11 @@ def _build_block(layer: LayerSpec, width: int) -> Block:
 class Model:
     def __init__(self, spec: ModelSpec):
         self.spec = spec
-        self.embedding = TokenEmbedding(spec.embedding)
+        self.embedding = get_part("embedding", spec.embedding.kind)(spec.embedding)
         self.position = get_part("position", spec.position.kind)(spec.position)
         self.blocks: List[Block] = [_build_block(l, spec.width) for l in spec.layers]
         self.final_norm = get_part("norm", spec.final_norm.kind)(spec.final_norm)
-        self.head = OutputHead(spec.head)
+        self.head = get_part("head", spec.head.kind)(spec.head)
         self.schedule = list(spec.schedule)
         for call in self.schedule:
             if not (0 <= call.layer < len(self.blocks)):
@@ -84,7 +83,9 @@ class Model:
         for part, pspec in self._parts():
             local = {l: tensors[pspec.tensors[l]] for l in part.requests()}
             if part is self.head:
-                part.bind(local, device, dtype, tied_weight=self.embedding.weight if self.head.tied else None)
+                # a head that shares the token table says so with `tied`; it gets the bound table
+                tied = getattr(self.head, "tied", False)
+                part.bind(local, device, dtype, tied_weight=self.embedding.table() if tied else None)
             else:
                 part.bind(local, device, dtype)
 
@@ -109,11 +110,13 @@ class Model:
         return self.position.max_positions
 
     def weight_bytes(self) -> int:
-        """Bytes of weights a decode step reads once: every layer's matrices and the head."""
-        total = self.head.weight_bytes()
+        """Bytes of weights a decode step reads once: every layer call's parts and the head (each
+        part reports its own; a part that reports nothing counts as 0)."""
+        total = self.head.weight_bytes() + self.final_norm.weight_bytes()
         for call in self.schedule:
             b = self.blocks[call.layer]
             total += b.mixer.weight_bytes() + b.feed_forward.weight_bytes()
+            total += sum(n.weight_bytes() for n in b.norms.values())
         return total
 
     # ---- the forward pass over one step's tokens ---------------------------------------

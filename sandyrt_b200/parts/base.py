@@ -16,6 +16,9 @@ Families and what each must provide:
                   forward(ctx, h, x, call) -> None   (x += mix(h), in place)
   FeedForward     forward(ctx, h, x) -> None         (x += ff(h), in place)
   Block           forward(ctx, x, call) -> None      (runs its norms, mixer, feed-forward)
+  Embedding       forward(ctx, x, status) -> None    (x = the tokens' rows, position table added)
+                  table() -> the bound token table
+  Head            forward(ctx, y, logits) -> None    (float32 logits of the normed rows y)
 
 `x` is the residual stream: float32 [tokens, width] in both compute dtypes, so the
 residual sum is always formed and kept in 32-bit.  `h` is a normed copy in the compute
@@ -125,6 +128,11 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         """Receive the tensors named by `requests` (host tensors) and place them on the device."""
 
+    def weight_bytes(self) -> int:
+        """Bytes of weights one step reads from this part (used for roofline figures); parts
+        with matrices override it."""
+        return 0
+
     # helpers ---------------------------------------------------------------------------
     def _param(self, key: str, kind=None, default=dataclasses.MISSING):
         if key not in self.params:
@@ -149,6 +157,29 @@ class PositionEncoding(Part):
 
     def rotate(self, ctx: StepContext, q: torch.Tensor, k: Optional[torch.Tensor]) -> None:
         return None
+
+
+class Embedding(Part):
+    """Token ids to the first residual stream.  `table()` is the bound token table (a head that
+    is tied to it multiplies by the same tensor)."""
+
+    def table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def forward(self, ctx: "StepContext", x: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """The last normed rows to float32 logits.  `tied` says that it shares the embedding's table
+    (its `bind` then receives `tied_weight`)."""
+    tied = False
+
+    def bind(self, tensors, device, dtype, tied_weight: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+    def forward(self, ctx: "StepContext", y: torch.Tensor, logits: torch.Tensor) -> None:
+        raise NotImplementedError
 
 
 class Mixer(Part):

@@ -16,11 +16,12 @@ import torch
 from ..csrc import ops
 from ..models.spec import PartSpec
 from ..weights.loader import TensorRequest
-from .base import Part, StepContext
+from ..registry import register_part
+from .base import Embedding, Head, StepContext
 from .linear import Linear
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.vocab_size = int(self._param("vocab_size"))
@@ -33,12 +34,18 @@ class TokenEmbedding(Part):
     def bind(self, tensors, device, dtype) -> None:
         self.weight = tensors["weight"].to(device=device, dtype=dtype).contiguous()
 
+    def table(self) -> Optional[torch.Tensor]:
+        return self.weight
+
+    def weight_bytes(self) -> int:
+        return 0        # a step reads a few rows of the table, not the table
+
     def forward(self, ctx: StepContext, x: torch.Tensor, status: Optional[torch.Tensor]) -> None:
         table = ctx.position.table() if ctx.position is not None else None
         ops.embed_positions(ctx.token_ids, ctx.positions, self.weight, table, x, status=status)
 
 
-class OutputHead(Part):
+class OutputHead(Head):
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.vocab_size = int(self._param("vocab_size"))
@@ -64,3 +71,7 @@ class OutputHead(Part):
 
     def weight_bytes(self) -> int:
         return self.linear.weight_bytes()
+
+
+register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("head", "output_head", OutputHead)

@@ -112,9 +112,9 @@ class Linear:
                     a = None
                 else:
                     a = a.tensor()
-            if norm is None and kv is None and rows > ops.SKINNY_NORM_MAX_ROWS and \
-                    ops.small_gemm_prefers_tc(a, self.weight, self.bias, out, act=act, residual=residual):
-                ops.gemm_tc(a, self.weight, self.bias, out, act=act, residual=residual)
+            if norm is None and kv is None and \
+                    ops.small_gemm_prefers_tc(rows, self.out_features, self.in_features):
+                ops.gemm_tc(a, self.weight, self.bias, out, act=act, residual=residual, tile_n=64)
                 return
             ops.gemm_skinny(a, self.weight, self.bias, out, act=act, residual=residual, norm=norm, kv=kv)
             if kv is not None:

@@ -37,6 +37,9 @@ class LayerNorm(Norm):
         self.gamma = tensors["weight"].to(device=device, dtype=dtype).contiguous()
         self.beta = tensors["bias"].to(device=device, dtype=dtype).contiguous() if self.has_bias else None
 
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.gamma, self.beta) if t is not None)
+
     def forward(self, ctx: StepContext, x: torch.Tensor, out: torch.Tensor,
                 rows: Optional[torch.Tensor] = None) -> None:
         ops.layernorm(x, self.gamma, self.beta, self.eps, out, rows=rows)

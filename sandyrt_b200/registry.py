@@ -24,7 +24,7 @@ class Architecture:
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
-_PART_KINDS = ("mixer", "feed_forward", "norm", "position", "block")
+_PART_KINDS = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
 _PARTS: Dict[str, Dict[str, type]] = {k: {} for k in _PART_KINDS}
 
 
@@ -48,7 +48,7 @@ def architectures():
 
 def register_part(family: str, kind: str, cls: type) -> None:
     """Register class `cls` as the implementation of part `kind` in `family`
-    ("mixer", "feed_forward", "norm", "position" or "block")."""
+    ("mixer", "feed_forward", "norm", "position", "block", "embedding" or "head")."""
     if family not in _PARTS:
         raise KeyError(f"unknown part family {family!r}; one of {_PART_KINDS}")
     _PARTS[family][kind] = cls

@@ -7,10 +7,12 @@ Here the model states every tensor it wants with its shape up front, the file is
 against that list in one pass, and ONE WeightBindingError lists everything that is wrong:
 missing tensors, unexpected tensors, and tensors of the wrong shape.
 
-Storage dtypes on the host after loading: F16 and BF16 -> bfloat16; a tensor stored in
-32-bit float stays float32; I32/I64/U8/BOOL tables -> int32.  The parts cast what feeds
-their matrix products to the engine's compute dtype when they bind; a part may ask that a
-tensor stored in 32-bit stays so (`keep_32bit`).
+Storage dtypes on the host after loading: floating-point tensors stay as the file stores them
+(BF16, F16 or F32: views of the mapping, nothing is rounded here); I32/I64/U8/BOOL tables ->
+int32.  The parts cast what feeds their matrix products to the engine's compute dtype when
+they bind, so each value is rounded at most once: an F16 file is widened exactly for the
+float32 path and rounded to bfloat16 for the bfloat16 path.  A part may ask that a tensor
+stored in 32-bit stays so (`keep_32bit`).
 """
 from __future__ import annotations
 
@@ -75,9 +77,7 @@ def _detect_prefix(names: Iterable[str], wanted: Iterable[str], prefixes: Sequen
 
 
 def _host_dtype(t: torch.Tensor) -> torch.Tensor:
-    if t.dtype == torch.float16:
-        return t.to(torch.bfloat16)
-    if t.dtype in (torch.bfloat16, torch.float32, torch.int32):
+    if t.dtype in (torch.float16, torch.bfloat16, torch.float32, torch.int32):
         return t
     if t.dtype in (torch.int64, torch.uint8, torch.bool):
         return t.to(torch.int32)

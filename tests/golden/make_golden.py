@@ -23,7 +23,7 @@ attribute of `__attention`) are all exercised.
 Weights are NOT stored: `golden_weights(case)` below regenerates them from the seed with
 numpy's PCG64, and the test calls the same function.
 
-    python tests/golden/make_golden.py [--reference /root/reference] [--build-dir /tmp/sandy_ref_build]
+    python tests/golden/make_golden.py --reference <checkout of sunho/SandyRT> [--build-dir DIR]
 """
 import argparse
 import json
@@ -183,10 +183,10 @@ def build_runner(reference, build_dir):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
-    ap.add_argument("--build-dir", default=os.path.join(tempfile.gettempdir(), "sandy_ref_build"))
+    ap.add_argument("--reference", required=True, help="a checkout of sunho/SandyRT")
+    ap.add_argument("--build-dir", default=None, help="where cpu_runner is built (default: a fresh temporary folder)")
     args = ap.parse_args()
-    runner = build_runner(args.reference, args.build_dir)
+    runner = build_runner(args.reference, args.build_dir or tempfile.mkdtemp(prefix="sandy_ref_build_"))
     for name, case in CASES.items():
         w = golden_weights(case)
         ids = w.pop("__ids__")

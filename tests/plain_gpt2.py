@@ -204,9 +204,11 @@ class PlainGPT2:
         self.w = w
         self.store = store
 
-    def logits(self, ids: Sequence[int]) -> np.ndarray:
+    def logits(self, ids: Sequence[int], rows: Optional[Sequence[int]] = None) -> np.ndarray:
         """src/models/gpt2_small.sandy.go:47-59: x = wte[ids] + wpe[0..T-1]; blocks; ln_f;
-        logits = x @ wte^T for every position.  Returns float32 [T, vocab]."""
+        logits = x @ wte^T for every position.  Returns float32 [T, vocab], or only the given
+        rows of it (the final norm and the head work row by row, so leaving rows out changes
+        nothing in the others)."""
         cfg, w = self.cfg, self.w
         T = len(ids)
         if T > cfg["n_positions"]:
@@ -215,6 +217,8 @@ class PlainGPT2:
              + embedding(range(T), w["wpe.weight"]).astype(np.float64)).astype(np.float32)
         for i in range(cfg["n_layer"]):
             x = block(x, w, i, cfg, self.store)
+        if rows is not None:
+            x = x[np.asarray(list(rows), dtype=np.int64)]
         y = _store(layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], cfg["layer_norm_epsilon"]), self.store)
         head = w["wte.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
         return (y.astype(np.float64) @ head.astype(np.float64).T).astype(np.float32)
@@ -283,7 +287,7 @@ def generate_greedy(model: PlainGPT2, prompt: Sequence[int], max_tokens: int,
     if max_tokens == 0:
         return out, "length"
     while True:
-        nxt = sample_token(model.logits(ids)[-1])
+        nxt = sample_token(model.logits(ids, rows=[len(ids) - 1])[0])
         out.append(nxt)
         ids.append(nxt)
         if nxt in stop_ids:

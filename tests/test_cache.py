@@ -155,7 +155,7 @@ def test_decode_splits_avoid_clusters_of_six_and_seven():
     for tokens in range(1, 80):
         for heads in (1, 2, 12, 16, 25):
             for max_kv in (64, 128, 512, 1024, 8192):
-                n = decode_splits(tokens, heads, max_kv)
+                n = decode_splits(tokens, heads, max_kv, sms=148)
                 assert n >= 1 and n not in (6, 7)
                 assert n <= max(1, max_kv // 64) or n == 5
                 seen.add(n)

@@ -216,3 +216,27 @@ def test_bursts_queued_ahead_give_the_same_tokens(model_dirs):
     assert llm.result(first).output_ids == ref.generate(prompts[1], max_tokens=60)[0].output_ids
     assert llm.result(second).output_ids == ref.generate(prompts[2], max_tokens=20)[0].output_ids
     llm.engine.cache.alloc.check()
+
+
+def test_a_recorded_burst_serves_a_batch_whose_member_was_replaced(model_dirs):
+    """A whole burst of decode steps is recorded as one graph once its shape has come by three
+    times.  Here three requests decode together long enough for that; then one of them ends and
+    a waiting request of another length takes its place, so the same burst shape comes by again
+    with another member at another position.  The tokens must equal those of single steps."""
+    prompts = _prompts("B", [21, 34, 9, 50], seed=41)
+    limits = [75, 75, 33, 40]
+
+    def run(max_burst):
+        llm = _llm(model_dirs["B"], max_live=3, max_burst=max_burst)
+        rids = [llm.add_request(p, max_tokens=m) for p, m in zip(prompts, limits)]
+        while llm.has_work() or llm._inflight is not None:
+            llm.step()
+        return llm, [llm.result(r).output_ids for r in rids]
+
+    single, want = run(1)
+    burst, got = run(8)
+    assert got == want
+    assert [len(g) for g in got] == limits
+    assert burst.engine.burst_graphs_recorded > 0, "no whole-burst graph was recorded"
+    burst.engine.check_status()
+    burst.engine.cache.alloc.check()

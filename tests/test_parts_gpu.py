@@ -332,3 +332,158 @@ def test_toy_model_with_stateful_mixer_registers_builds_and_steps(tmp_path):
     for k in seqs:
         np.testing.assert_allclose(np.concatenate(got[k]), want[k], atol=3e-5, rtol=1e-4, err_msg=f"sequence {k}")
     assert eng.cache.alloc.free_slots() == 3
+
+
+def test_a_reused_state_slot_starts_from_zero_through_the_entry_point(tmp_path):
+    """Generation admits requests through the scheduler.  With one slot, the second request gets
+    the slot the first one left; its fixed-size state must start as zeros, so its tokens equal
+    those of the same request on a fresh engine."""
+    from sandyrt_b200.engine.llm import LLM
+    from sandyrt_b200.weights.random_init import write_random_model
+
+    ToyConfig = _register_toy()
+    cfg = ToyConfig(width=32, vocab_size=90, decay=0.95)
+    d = write_random_model(cfg, str(tmp_path / "toy"), seed=4, dtype=torch.float32)
+    rng = np.random.default_rng(1)
+    first, second = rng.integers(0, 90, size=19).tolist(), rng.integers(0, 90, size=7).tolist()
+    llm = LLM(d, dtype="float32", cache_tokens=256, page_size=8, max_live=1)
+    both = llm.generate([first, second], max_tokens=10)
+    alone = LLM(d, dtype="float32", cache_tokens=256, page_size=8, max_live=1).generate(second, max_tokens=10)
+    assert both[1].output_ids == alone[0].output_ids
+    w = plain.read_safetensors(os.path.join(d, "model.safetensors"))
+    ids = list(second)
+    for tok in both[1].output_ids:
+        assert tok == int(np.argmax(_toy_plain_logits(w, ids, 0.95, 32)[-1]))
+        ids.append(tok)
+
+
+# ---- a position encoding that acts on queries and keys ----------------------------------------
+def _register_rotary():
+    """Registers, from outside the framework, a position encoding that turns pairs of query and
+    key channels by an angle that grows with the position, and a two-layer architecture using
+    it.  The attention part then cannot let its projection write keys into the pages (they are
+    turned first): it rotates, appends with the separate key/value write, and attends."""
+    from sandyrt_b200.config.base import ModelConfig
+    from sandyrt_b200.models.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
+    from sandyrt_b200.parts.base import PositionEncoding
+    from sandyrt_b200.registry import register_architecture, register_part
+
+    class ToyRotary(PositionEncoding):
+        rotates = True
+        graph_safe = False
+        max_positions = None
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.head_dim, self.base = int(self.params["head_dim"]), float(self.params["base"])
+
+        def _turn(self, ctx, t):
+            T, D = t.shape[0], self.head_dim
+            x = t.float().reshape(T, -1, D // 2, 2)
+            freq = self.base ** (-torch.arange(D // 2, device=t.device, dtype=torch.float32) / (D // 2))
+            ang = ctx.positions.to(torch.float32)[:, None, None] * freq[None, None, :]
+            c, s = torch.cos(ang), torch.sin(ang)
+            y = torch.stack((x[..., 0] * c - x[..., 1] * s, x[..., 0] * s + x[..., 1] * c), dim=-1)
+            t.copy_(y.reshape(T, -1).to(t.dtype))
+
+        def rotate(self, ctx, q, k):
+            self._turn(ctx, q)
+            if k is not None:
+                self._turn(ctx, k)
+
+    @dataclasses.dataclass(frozen=True)
+    class RotaryConfig(ModelConfig):
+        architecture = "ToyRotaryModel"
+        width: int = 0
+        vocab_size: int = 0
+        n_heads: int = 0
+        base: float = 100.0
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(width=raw["width"], vocab_size=raw["vocab_size"], n_heads=raw["n_heads"], base=raw["base"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "width": self.width, "vocab_size": self.vocab_size,
+                    "n_heads": self.n_heads, "base": self.base}
+
+        def validate(self):
+            assert (self.width // self.n_heads) % 16 == 0
+
+    def describe(cfg):
+        E, H = cfg.width, cfg.n_heads
+        D = E // H
+        norm = lambda n: PartSpec("layernorm", {"width": E, "eps": 1e-5}, {"weight": n + ".g", "bias": n + ".b"})
+        layers = []
+        for i in range(2):
+            p = f"l{i}."
+            layers.append(LayerSpec(
+                "pre_norm",
+                PartSpec("causal_attention", {"width": E, "n_heads": H, "n_kv_heads": H, "head_dim": D,
+                                              "scale": 1 / math.sqrt(D), "weight_layout": "out_in"},
+                         {"qkv.weight": p + "qkv.w", "qkv.bias": p + "qkv.b", "out.weight": p + "o.w",
+                          "out.bias": p + "o.b"}),
+                PartSpec("dense_mlp", {"width": E, "inner": 2 * E, "activation": "gelu", "weight_layout": "out_in"},
+                         {"up.weight": p + "up.w", "up.bias": p + "up.b", "down.weight": p + "dn.w",
+                          "down.bias": p + "dn.b"}),
+                {"mixer": norm(p + "n1"), "feed_forward": norm(p + "n2")}))
+        return ModelSpec(architecture=cfg.architecture, width=E, vocab_size=cfg.vocab_size, max_positions=None,
+                         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "width": E}, {"weight": "emb"}),
+                         position=PartSpec("toy_rotary", {"head_dim": D, "base": cfg.base}, {}),
+                         layers=layers, schedule=[LayerCall(0, 0), LayerCall(1, 1)], final_norm=norm("nf"),
+                         head=PartSpec("output_head", {"vocab_size": cfg.vocab_size, "width": E, "tied": True}, {}))
+
+    register_part("position", "toy_rotary", ToyRotary)
+    register_architecture("ToyRotaryModel", RotaryConfig, describe)
+    return RotaryConfig
+
+
+def _rotary_plain_logits(w, ids, E, H, base, rnd):
+    T, D = len(ids), E // H
+    x = plain.embedding(ids, w["emb"])
+    ln = lambda x, n: plain.layer_norm(x, w[n + ".g"], w[n + ".b"], 1e-5)
+    lin = lambda h, p: plain.linear_in_out(h, rnd(w[p + "w"]).T, rnd(w[p + "b"]))
+    freq = base ** (-np.arange(D // 2, dtype=np.float32) / (D // 2))
+    ang = np.arange(T, dtype=np.float32)[:, None, None] * freq[None, None, :]
+    c, s = np.cos(ang), np.sin(ang)
+
+    def turn(t):
+        v = t.reshape(T, H, D // 2, 2)
+        return np.stack((v[..., 0] * c - v[..., 1] * s, v[..., 0] * s + v[..., 1] * c), axis=-1).reshape(T, E)
+
+    split = lambda t: t.reshape(T, H, D).transpose(1, 0, 2)
+    for i in range(2):
+        p = f"l{i}."
+        qkv = rnd(lin(rnd(ln(x, p + "n1")), p + "qkv."))
+        q, k, v = rnd(turn(qkv[:, :E])), rnd(turn(qkv[:, E:2 * E])), qkv[:, 2 * E:]
+        o = plain.causal_attention(split(q), split(k), split(v), 1 / math.sqrt(D)).transpose(1, 0, 2).reshape(T, E)
+        x = x + lin(rnd(o), p + "o.")
+        x = x + lin(rnd(plain.gelu_erf(lin(rnd(ln(x, p + "n2")), p + "up."))), p + "dn.")
+    return rnd(ln(x, "nf")) @ rnd(w["emb"]).T
+
+
+@pytest.mark.parametrize("dtype,atol,rtol", [("float32", 3e-5, 1e-4), ("bfloat16", 6e-3, 2e-2)])
+def test_position_encoding_that_rotates_queries_and_keys(tmp_path, dtype, atol, rtol):
+    from sandyrt_b200.engine.step import Engine, StepEntry
+    from sandyrt_b200.models.model import load_model
+    from sandyrt_b200.weights.random_init import write_random_model
+
+    RotaryConfig = _register_rotary()
+    cfg = RotaryConfig(width=96, vocab_size=130, n_heads=3, base=50.0)
+    d = write_random_model(cfg, str(tmp_path / "rot"), seed=6, dtype=torch.float32)
+    model = load_model(d, device=DEV, dtype=getattr(torch, dtype))
+    assert model.max_positions is None and not model.graph_safe
+    eng = Engine(model, max_tokens=256, page_size=8, max_requests=2)
+    eng.cache.device_caches.poison()
+    w = plain.read_safetensors(os.path.join(d, "model.safetensors"))
+    ids = np.random.default_rng(2).integers(0, 130, size=45).tolist()
+    rnd = plain.round_bf16 if dtype == "bfloat16" else (lambda a: a)
+    want = _rotary_plain_logits(w, ids, 96, 3, 50.0, rnd)
+    for cuts in ([45], [20, 2, 1, 1, 21], [1] * 6 + [39]):
+        rows, pos = [], 0
+        for n in cuts:
+            rows.append(eng.step([StepEntry("r", ids[pos:pos + n], list(range(n)))]).cpu().numpy().copy())
+            pos += n
+        eng.release("r")
+        np.testing.assert_allclose(np.concatenate(rows), want, atol=atol, rtol=rtol, err_msg=f"cuts {cuts}")
+    eng.check_status()

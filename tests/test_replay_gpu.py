@@ -153,3 +153,40 @@ def test_mixed_requests_with_page_reuse(model_dirs, plain_models, name, dtype):
     assert total_pages_if_never_reused > 12          # so pages were used again
     for r, ids in enumerate(prompts):
         _close(np.concatenate(got[r], axis=0), want_logits[r], dtype, f"tiny {name} mixed request {r}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_recorded_prompt_step_serves_other_divisions_of_its_tokens(model_dirs, plain_models, dtype):
+    """A prompt step is recorded as a CUDA graph under a key of counts (tokens, requests, wanted
+    rows, longest portion, block-table width) and replayed for any step with the same counts.
+    Three steps with the same counts divide their 48 tokens differently among three requests
+    and start at different places of them; the later ones are served by the recording, and every
+    row must still be right: whatever a launch takes from the host's lists would be stale."""
+    from sandyrt_b200.engine.step import StepEntry
+
+    name = "B"
+    eng = _engine(model_dirs[name], dtype, max_tokens=512, page_size=16)
+    plain = plain_models(name, STORE[dtype])
+    prompts = _prompts(name, [72, 72, 80], seed=13)
+    want = [plain.logits(p) for p in prompts]
+    fed = [0, 0, 0]
+    got = [[], [], []]
+    replays = []
+    for division in ([16, 8, 24], [8, 16, 24], [24, 24, 0], [24, 16, 8], [0, 8, 24]):
+        entries = [StepEntry(r, prompts[r][fed[r]:fed[r] + n], list(range(n)))
+                   for r, n in enumerate(division) if n]
+        before = eng.graph_replays
+        out = eng.step(entries).cpu().numpy()
+        replays.append(eng.graph_replays - before)
+        row = 0
+        for e in entries:
+            n = len(e.tokens)
+            got[e.rid].append(out[row:row + n].copy())
+            row += n
+            fed[e.rid] += n
+    eng.check_status()
+    # steps 0, 1 and 3 share one key (48 tokens, 3 requests, longest 24): the second records, the
+    # third sight replays; steps 2 and 4 have other counts
+    assert replays[1] == 1 and replays[3] == 1
+    for r in range(3):
+        _close(np.concatenate(got[r], axis=0), want[r][:fed[r]], dtype, f"request {r} under a replayed prompt graph")
