@@ -121,7 +121,12 @@ class LLM:
         return rid
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        """Whether a call of `step` would do anything: a request is waiting or running, or a burst
+        queued on the device has not been read yet."""
+        return self.scheduler.has_work() or self._inflight is not None
+
+    def finished(self, rid: Hashable) -> bool:
+        return self._requests[rid].state is RequestState.FINISHED
 
     def _burst_length(self, plan: StepPlan) -> int:
         """How many decode steps may run on the device before the host looks again: more than
