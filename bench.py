@@ -1,15 +1,20 @@
 """Benchmark of the engine: decode tokens per second, prefill tokens per second, rooflines.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload medium|xl          the mixed-batch workloads through LLM.generate
+    python bench.py --profile-kernels             time per kernel class of a decode and a prompt step
+    python bench.py --micro gemm|decode-attention|prefill-attention [...]   kernel micro-benchmarks
 
-Default workload: GPT-2 small (12 layers, width 768, 12 heads of 64, inner 3072, vocabulary
-50257, 1024 positions) with seeded random weights in bfloat16, a batch of 8 requests with
-128-token prompts of uniform random ids; one "step" is one decode step of the whole batch.
-Prints ONE JSON line.  `value` is decoded tokens per second timed on the device over K
-steps; `e2e` is the same through the Python entry point (LLM.add_request/step: host token
-ids in, every step's drawn tokens read back to the host); `prefill` is one step over 2,048
-prompt tokens (2 prompts x 1,024); `roofline` relates the decode step to HBM bandwidth;
-`points` holds decode tokens per second at batch 1 and 64.
+Default workload: GPT-2 small (12 layers, width 768, 12 heads of 64, inner 3072, vocabulary 50257,
+1024 positions) with seeded random weights in bfloat16, a batch of 8 requests with 128-token prompts
+of uniform random ids; one "step" is one decode step of the whole batch.  Prints ONE JSON line.
+`value` is decoded tokens per second timed on the device over K steps (CUDA events on the engine's
+stream around bursts queued behind bursts that are still running); `e2e` is the same through the
+Python entry point (LLM.add_request/step: host token ids in, every step's drawn tokens read back to
+the host), on the wall clock; `prefill` is one step over 2,048 prompt tokens (2 prompts x 1,024);
+`roofline` relates the decode step to HBM bandwidth; `points` holds decode at batch 1 and 64, each
+with its context, step time and roofline fraction; `fp32` holds the float32 path's decode at batch
+1 and 8 and its prefill.
 
 The engine runs on one GPU: for --gpus N > 1 it prints one line that says so and exits 2.
 """
@@ -20,16 +25,12 @@ import json
 import os
 import subprocess
 import sys
-import tempfile
 import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# GPT-2 small: experiments/gpt2_small/config.json of the reference
-SMALL = dict(n_layer=12, n_embd=768, n_head=12, n_positions=1024, vocab_size=50257, n_inner=3072,
-             layer_norm_epsilon=1e-5, activation_function="gelu_new")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -45,6 +46,12 @@ def load_peaks():
         except (KeyError, ValueError, json.JSONDecodeError):
             pass
     return dict(FALLBACK_PEAKS)
+
+
+def load_model_config(name: str) -> dict:
+    """configs/gpt2_<name>.json: the config.json of the named size."""
+    with open(os.path.join(ROOT, "configs", f"gpt2_{name}.json")) as f:
+        return json.load(f)
 
 
 class ClockSampler:
@@ -105,19 +112,17 @@ def reference_arm():
     return 0
 
 
-def make_model(n_layer: int, seed: int = 0):
+def make_model(raw_config: dict, n_layer: int, dtype_name: str, seed: int = 0):
+    """A model of the named configuration (with n_layer layers) with seeded random weights."""
     import torch
 
     from sandyrt_b200.config.gpt2 import GPT2Config
-    from sandyrt_b200.models.model import build_model, describe
-    from sandyrt_b200.weights.random_init import random_tensors
+    from sandyrt_b200.models.model import build_model
 
-    cfg = GPT2Config(**{**SMALL, "n_layer": n_layer})
+    cfg = GPT2Config.from_dict({**raw_config, "n_layer": n_layer})
     cfg.validate()
-    model = build_model(describe(cfg))
-    tensors = random_tensors(model.tensor_requests(), seed, torch.bfloat16)
-    model.bind(tensors, "cuda:0", torch.bfloat16)
-    model.config = cfg
+    model = build_model(cfg)
+    model.bind_random(seed, getattr(torch, dtype_name))
     return model, cfg
 
 
@@ -125,8 +130,9 @@ def _start_decoding(llm, batch, prompt_len, max_tokens, warmup, rng, vocab):
     """Add `batch` requests, run their prompts and `warmup` decode steps through the entry point."""
     rids = [llm.add_request(rng.integers(0, vocab, size=prompt_len).tolist(), max_tokens=max_tokens)
             for _ in range(batch)]
-    while any(len(llm._requests[r].output) == 0 for r in rids):       # prefill
-        llm.step()
+    seen = set()
+    while len(seen) < batch:                                          # prefill
+        seen.update(r for r, _ in llm.step())
     for _ in range(warmup):
         llm.step()
     return rids
@@ -143,41 +149,42 @@ def _drop(llm, rids):
 def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, want_e2e=True):
     """Times `steps` decode steps of `batch` requests after `warmup` untimed ones, twice:
 
+    e2e:    through the entry point (LLM.step: scheduler, bursts of decode steps with the drawn
+            tokens of every step read back to the host), timed on the wall clock;
     device: the engine's decode bursts (a burst's index arrays, block tables and sampling options
             copied from pinned memory; per step the model and the sampler, which feeds the drawn
-            token to the next step on the device), bursts queued back to back with no read-back
-            in between, timed with CUDA events;
-    e2e:    the same number of steps through the entry point (LLM.step: scheduler, bursts of
-            decode steps with the drawn tokens of every step read back to the host), timed on
-            the wall clock.
+            token to the next step on the device), queued back to back with no read-back in
+            between.  Two untimed bursts are queued first and the first event is recorded BEHIND
+            them, so the timed bursts are queued while the device is still busy: what is between
+            the two events is device work only.
 
     Returns (device ms/step, (e2e ms/step, host-to-device and device-to-host bytes per step of that
-    loop), mean context length, launches per step)."""
+    loop), mean context length of the device loop, launches per step)."""
     import numpy as np
-    import torch
 
     from sandyrt_b200.engine.step import SampleRow, StepEntry
 
     e2e_ms, e2e_h2d, e2e_d2h = None, 0.0, 0.0
+    engine = llm.engine
     if want_e2e:
         rids = _start_decoding(llm, batch, prompt_len, steps + 10 * warmup + 80, warmup, rng, vocab)
-        torch.cuda.synchronize()
+        engine.synchronize()
         first = llm.decode_steps_run
-        h2d0, d2h0 = llm.engine.h2d_bytes_total, llm.engine.d2h_bytes_total
+        h2d0, d2h0 = engine.h2d_bytes_total, engine.d2h_bytes_total
         t0 = time.perf_counter()
-        while llm.decode_steps_run - first < steps:     # a call may run a burst of several steps
-            llm.step()
-        llm.drain()                                     # a burst queued ahead: its steps count, and so does its time
-        torch.cuda.synchronize()
-        n_steps = llm.decode_steps_run - first
+        n_steps = 0
+        while n_steps < steps:                          # a call may run a burst of several steps
+            n_steps += len(llm.step()) // batch
+        n_steps += len(llm.drain()) // batch            # a burst queued ahead: its steps count, and so does its time
+        engine.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / n_steps
-        e2e_h2d = (llm.engine.h2d_bytes_total - h2d0) / n_steps
-        e2e_d2h = (llm.engine.d2h_bytes_total - d2h0) / n_steps
+        assert llm.decode_steps_run - first == n_steps
+        e2e_h2d = (engine.h2d_bytes_total - h2d0) / n_steps
+        e2e_d2h = (engine.d2h_bytes_total - d2h0) / n_steps
         _drop(llm, rids)
 
     rids = _start_decoding(llm, batch, prompt_len, 100000, warmup, rng, vocab)
     llm.drain()                                          # the loop below drives the engine itself
-    engine = llm.engine
     ctx0 = sum(engine.length(r) for r in rids) / batch
     rows = [SampleRow() for _ in rids]
     burst = llm.max_burst
@@ -190,30 +197,135 @@ def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, want_e2e=True)
 
     # untimed (the entry point's warm-up above has already made the engine record this burst shape)
     in_flight = 0
-    for _ in range(2):
+    for _ in range(3):
         queue(burst, in_flight)
         in_flight += burst
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    engine.synchronize()
+    for _ in range(2):                                   # these keep the device busy while the timed ones are queued
+        queue(burst, in_flight)
+        in_flight += burst
+    before = in_flight
+    engine.mark(0)
     done = 0
     while done < steps:
         n = min(burst, steps - done)
         last = queue(n, in_flight)
         in_flight += n
         done += n
-    e1.record()
-    torch.cuda.synchronize()
+    engine.mark(1)
+    dev_ms = engine.elapsed_ms() / steps
     if (engine.burst_tokens(last) < 0).any():
         raise RuntimeError("the sampler reported bad logits")
     engine.check_status()
-    dev_ms = e0.elapsed_time(e1) / steps
     for r in rids:
         engine.commit(r, engine.length(r) + in_flight)
-    ctx1 = sum(engine.length(r) for r in rids) / batch
+    mean_ctx = ctx0 + before + 0.5 * steps               # the context of the timed steps
     launches = engine.last_launches
     _drop(llm, rids)
-    return dev_ms, (e2e_ms, e2e_h2d, e2e_d2h), 0.5 * (ctx0 + ctx1), launches
+    return dev_ms, (e2e_ms, e2e_h2d, e2e_d2h), mean_ctx, launches
+
+
+def prefill_run(engine, vocab, rng, n_prompts=2, prompt_len=1024, reps=5):
+    """Median device time of one step over n_prompts x prompt_len prompt tokens."""
+    from sandyrt_b200.engine.step import StepEntry
+
+    prompts = [rng.integers(0, vocab, size=prompt_len).tolist() for _ in range(n_prompts)]
+    times = []
+    for it in range(3 + reps):
+        entries = [StepEntry(f"p{it}-{i}", p, [len(p) - 1]) for i, p in enumerate(prompts)]
+        engine.mark(0)
+        engine.step(entries)
+        engine.mark(1)
+        if it >= 3:
+            times.append(engine.elapsed_ms())
+        for e in entries:
+            engine.release(e.rid)
+    engine.check_status()
+    return sorted(times)[len(times) // 2]
+
+
+def prefill_flops(cfg, n_prompts, prompt_len):
+    E, I, L, V = cfg.n_embd, cfg.inner_dim, cfg.n_layer, cfg.vocab_size
+    T = n_prompts * prompt_len
+    gemm = 2.0 * T * L * (E * 3 * E + E * E + 2 * E * I) + 2.0 * n_prompts * E * V
+    attn = L * n_prompts * (2.0 * 2 * E * (prompt_len * (prompt_len + 1) / 2))     # QK^T and PV over the causal half
+    return gemm + attn
+
+
+def roofline_of(llm, model, batch, ctx, ms, peaks):
+    weight_bytes = model.weight_bytes()
+    kv_bytes = llm.engine.cache.kv_bytes_per_token() * batch * ctx
+    gbs = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
+    return {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+            "of": peaks["source"], "bytes_per_step": weight_bytes + kv_bytes}
+
+
+def workload(name: str, dtype_name: str, layers: int) -> int:
+    """The mixed-batch workloads through LLM.generate.
+    medium: 32 requests, prompt lengths uniform in [16, 768], 256 tokens each.
+    xl:     64 requests, prompt lengths uniform in [64, 512], 256 tokens each, 16-token pages."""
+    import numpy as np
+
+    from sandyrt_b200.engine.llm import LLM
+
+    raw = load_model_config(name)
+    n_req, lo, hi = (32, 16, 768) if name == "medium" else (64, 64, 512)
+    model, cfg = make_model(raw, layers or raw["n_layer"], dtype_name)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).tolist() for n in rng.integers(lo, hi + 1, size=n_req)]
+    llm = LLM(model, dtype=dtype_name, cache_tokens=n_req * 1024, page_size=16, max_live=n_req, max_step_tokens=4096,
+              prefill_chunk_tokens=2048)
+    llm.generate([p[:32] for p in prompts[:4]], max_tokens=24)              # warm-up: kernels built, graphs recorded
+    t0 = time.perf_counter()
+    results = llm.generate(prompts, max_tokens=256)
+    llm.engine.synchronize()
+    wall = time.perf_counter() - t0
+    out_tokens = sum(r.completion_tokens for r in results)
+    print(json.dumps({
+        "workload": name, "dtype": dtype_name, "requests": n_req, "prompt_tokens": sum(len(p) for p in prompts),
+        "generated_tokens": out_tokens, "wall_s": wall, "tokens_per_s": out_tokens / wall,
+        "total_tokens_per_s": (out_tokens + sum(len(p) for p in prompts)) / wall,
+        "preemptions": llm.scheduler.stats["preemptions"], "steps": llm.scheduler.stats["steps"],
+        "pages_high_water": [p.high_water for p in llm.engine.cache.alloc.pools], "page_size": 16,
+        "n_layer": cfg.n_layer, "n_layer_full": raw["n_layer"], "n_embd": cfg.n_embd, "weights": "random seed 0"}))
+    return 0
+
+
+def profile_kernels(dtype_name: str, layers: int, batch: int) -> int:
+    """Device time per kernel class of one decode step and one 2,048-token prompt step (eager
+    launches with a pair of CUDA events around each, so launch gaps are not in the figures)."""
+    import numpy as np
+
+    from sandyrt_b200 import core
+    from sandyrt_b200.engine.step import Engine, StepEntry
+
+    raw = load_model_config("small")
+    model, cfg = make_model(raw, layers or raw["n_layer"], dtype_name)
+    engine = Engine(model, max_tokens=batch * 512 + 4096, max_requests=max(batch, 2), max_step_tokens=4096,
+                    use_cuda_graphs=False)
+    rng = np.random.default_rng(0)
+    ids = lambda n: rng.integers(0, cfg.vocab_size, size=n).tolist()
+    for i in range(batch):
+        engine.step([StepEntry(i, ids(300), [])])
+    decode = lambda: engine.step([StepEntry(i, ids(1), [0]) for i in range(batch)])
+    prompt = lambda k: (engine.step([StepEntry(f"p{k}a", ids(1024), [1023]), StepEntry(f"p{k}b", ids(1024), [1023])]),
+                        engine.release(f"p{k}a"), engine.release(f"p{k}b"))
+    for what, fn, reps in (("decode step, batch %d at context ~300" % batch, lambda k: decode(), 5),
+                           ("prompt step, 2 x 1,024 tokens", prompt, 3)):
+        fn(-1)                                            # untimed: kernels loaded, products tuned
+        core.call("global", None, "profile_kernels", enable=True)
+        for k in range(reps):
+            fn(k)
+        table = core.call("global", None, "profile_kernels", enable=False)
+        total = sum(r["us"] for r in table) / reps
+        print(f"{what} ({dtype_name}, {cfg.n_layer} layers): {total:.1f} us in kernels per step")
+        print("  class                     calls      us   share    GB/s  TFLOP/s")
+        for r in sorted(table, key=lambda r: -r["us"]):
+            us = r["us"] / reps
+            gbs = r["bytes"] / reps / us / 1e3 if us else 0.0
+            tf = r["flops"] / reps / us / 1e6 if us else 0.0
+            print(f"  {r['class']:24s} {r['calls'] // reps:6d} {us:7.1f} {100 * us / total:6.1f}% {gbs:7.0f} {tf:8.1f}")
+    return 0
 
 
 def main() -> int:
@@ -224,25 +336,35 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=128)
-    ap.add_argument("--layers", type=int, default=SMALL["n_layer"])
-    ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="dtype of --workload / --profile-kernels")
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the float32 block")
+    ap.add_argument("--workload", choices=["medium", "xl"], help="run a mixed-batch workload through LLM.generate instead")
+    ap.add_argument("--profile-kernels", action="store_true", help="print device time per kernel class instead")
+    ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
         print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
         return 2
+    if args.micro is not None:
+        from sandyrt_b200.csrc import microbench
+        return microbench.main(args.micro)
+    if args.workload:
+        return workload(args.workload, args.dtype, args.layers)
+    if args.profile_kernels:
+        return profile_kernels(args.dtype, args.layers, args.batch)
     if args.warmup < 3:
         args.warmup = 3
 
     import numpy as np
-    import torch
 
     from sandyrt_b200.engine.llm import LLM
-    from sandyrt_b200.engine.step import StepEntry
 
     peaks = load_peaks()
-    model, cfg = make_model(args.layers)
+    raw = load_model_config("small")
+    model, cfg = make_model(raw, args.layers or raw["n_layer"], "bfloat16")
     vocab = cfg.vocab_size
     rng = np.random.default_rng(0)
     llm = LLM(model, cache_tokens=64 * 1024 + 4096, max_live=64, max_step_tokens=4096, prefill_chunk_tokens=2048)
@@ -251,76 +373,57 @@ def main() -> int:
     clocks = ClockSampler()
     clocks.start()
 
-    # ---- decode at the headline batch: device-timed step of the engine + sampler ------------
-    # The same loop gives the end-to-end number through the entry point.  While all requests are
-    # decoding, llm.step() runs bursts of up to 8 decode steps: a burst's index arrays, block
-    # tables and sampling options are packed into pinned memory and copied to the device, the
-    # sampler feeds each drawn token to the next step on the device, and every step's drawn
-    # tokens are copied back to pinned memory and handed to the scheduler; the next burst is
-    # queued before the last one's tokens are read.  The byte counts are those copies, per step.
-    dev_ms, (wall_ms, e2e_h2d, e2e_d2h), mean_ctx, launches_per_step = decode_run(llm, args.batch, args.prompt_len, args.steps,
-                                                              args.warmup, rng, vocab)
+    # ---- decode at the headline batch ------------------------------------------------------------
+    dev_ms, (wall_ms, e2e_h2d, e2e_d2h), mean_ctx, launches_per_step = decode_run(
+        llm, args.batch, args.prompt_len, args.steps, args.warmup, rng, vocab)
+    if dev_ms > wall_ms * 1.02:
+        raise RuntimeError(f"device time {dev_ms:.4f} ms a step exceeds the wall-clock {wall_ms:.4f} ms of the same work")
     value = args.batch / (dev_ms / 1e3)
     e2e_value = args.batch / (wall_ms / 1e3)
-    weight_bytes = model.weight_bytes()
-    kv_bytes = engine.cache.kv_bytes_per_token() * args.batch * mean_ctx
-    achieved_gbs = (weight_bytes + kv_bytes) / (dev_ms / 1e3) / 1e9
+    roofline = roofline_of(llm, model, args.batch, mean_ctx, dev_ms, peaks)
 
-    # ---- prefill of 2,048 tokens: 2 prompts x 1,024 in one step ------------------------------
-    T = 2048
-    prompts = [rng.integers(0, vocab, size=1024).tolist() for _ in range(2)]
-    prefill_ms = []
-    for it in range(3 + 5):
-        entries = [StepEntry(f"p{it}-{i}", p, [len(p) - 1]) for i, p in enumerate(prompts)]
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        engine.step(entries)
-        e1.record()
-        torch.cuda.synchronize()
-        if it >= 3:
-            prefill_ms.append(e0.elapsed_time(e1))
-        for e in entries:
-            engine.release(e.rid)
-    pf_ms = sorted(prefill_ms)[len(prefill_ms) // 2]
-    E, I, L, V = cfg.n_embd, cfg.inner_dim, cfg.n_layer, cfg.vocab_size
-    gemm_flops = 2.0 * T * L * (E * 3 * E + E * E + 2 * E * I) + 2.0 * 2 * E * V
-    attn_flops = L * 2 * (2.0 * 2 * E * (1024 * 1025 / 2))      # QK^T and PV over the causal half, 2 prompts
-    pf_flops = gemm_flops + attn_flops
-    pf_frac = pf_flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)
+    # ---- prefill of 2,048 tokens: 2 prompts x 1,024 in one step ----------------------------------
+    pf_ms = prefill_run(engine, vocab, rng)
+    pf_frac = prefill_flops(cfg, 2, 1024) / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)
 
-    points = {}
+    points, fp32 = {}, {}
     if not args.skip_points:
         for b in (1, 64):
-            d_ms, _, _, _ = decode_run(llm, b, args.prompt_len, min(args.steps, 128), args.warmup, rng, vocab,
-                                       want_e2e=False)
-            points[f"decode_b{b}"] = b / (d_ms / 1e3)
+            d_ms, _, ctx, _ = decode_run(llm, b, args.prompt_len, min(args.steps, 128), args.warmup, rng, vocab, want_e2e=False)
+            points[f"decode_b{b}"] = {"value": b / (d_ms / 1e3), "ms_per_step": d_ms, "mean_context": round(ctx, 1),
+                                      "roofline_frac": roofline_of(llm, model, b, ctx, d_ms, peaks)["frac"]}
+        # the float32 path (FFMA products, float cache): the same model in float32
+        model32, _ = make_model(raw, args.layers or raw["n_layer"], "float32")
+        llm32 = LLM(model32, dtype="float32", cache_tokens=16 * 1024 + 4096, max_live=16, max_step_tokens=4096,
+                    prefill_chunk_tokens=2048)
+        for b in (1, 8):
+            d_ms, _, ctx, _ = decode_run(llm32, b, args.prompt_len, min(args.steps, 32), 3, rng, vocab, want_e2e=False)
+            fp32[f"decode_b{b}"] = {"value": b / (d_ms / 1e3), "ms_per_step": d_ms, "mean_context": round(ctx, 1)}
+        p32 = prefill_run(llm32.engine, vocab, rng, reps=2)
+        fp32["prefill"] = {"value": 2048 / (p32 / 1e3), "tokens": 2048, "ms": p32}
 
     clock_info = clocks.stop()
-    launches = launches_per_step * args.steps
     out = {
         "metric": "decode tok/s at batch 8 (GPT-2 small)", "value": value, "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "gpt2-small", "n_layer": cfg.n_layer, "n_layer_full": SMALL["n_layer"], "n_embd": E,
-                   "n_head": cfg.n_head, "head_dim": cfg.head_dim, "n_inner": I, "vocab_size": V,
+        "config": {"model": "gpt2-small", "n_layer": cfg.n_layer, "n_layer_full": raw["n_layer"], "n_embd": cfg.n_embd,
+                   "n_head": cfg.n_head, "head_dim": cfg.head_dim, "n_inner": cfg.inner_dim, "vocab_size": vocab,
                    "n_positions": cfg.n_positions, "global_batch": args.batch, "seq_len": cfg.n_positions,
-                   "prompt_len": args.prompt_len, "mean_context": round(mean_ctx, 1), "page_size": engine.cache.page_size,
-                   "parallelism": "single-gpu", "weights": "random seed 0",
-                   "l2": "inputs larger than L2 (weights %.0f MB)" % (weight_bytes / 1e6)},
+                   "prompt_len": args.prompt_len, "mean_context": round(mean_ctx, 1), "page_size": 16,
+                   "parallelism": "single-gpu", "weights": "random seed 0", "host": "C++ core (libsandy_core)",
+                   "l2": "inputs larger than L2 (weights %.0f MB)" % (model.weight_bytes() / 1e6)},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": wall_ms,
                 "h2d_bytes_per_step": round(e2e_h2d, 1), "d2h_bytes_per_step": round(e2e_d2h, 1),
-                "steps_per_burst": llm.max_burst, "bursts_queued_ahead": bool(llm.pipeline_bursts)},
-        "gpu_launches": launches,
-        "prefill": {"value": T / (pf_ms / 1e3), "tokens": T, "ms": pf_ms, "frac": pf_frac,
+                "steps_per_burst": 8, "bursts_queued_ahead": True},
+        "gpu_launches": launches_per_step * args.steps, "launches_per_step": launches_per_step,
+        "prefill": {"value": 2048 / (pf_ms / 1e3), "tokens": 2048, "ms": pf_ms, "frac": pf_frac,
                     "peak": f"{peaks['bf16_tflops']} TFLOP/s bf16 of {peaks['source']}"},
-        "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved_gbs / peaks["hbm_gbs"], "of": peaks["source"],
-                     "bytes_per_step": weight_bytes + kv_bytes},
+        "roofline": roofline,
         "points": points,
+        "fp32": fp32,
         "clocks": clock_info,
     }
-    print(f"[bench] graph replays {engine.graph_replays}, recorded graphs {len(engine._graphs)}, "
-          f"stale graphs dropped {engine.stale_graphs}", file=sys.stderr)
     print(json.dumps(out))
     return 0
 

@@ -1,3 +1,2 @@
-from .manager import CacheManager, DeviceCaches  # noqa: F401
 from .pages import (FREED, BlockAllocator, CacheError, CacheLayout, NoFreeSlot, OutOfPages,  # noqa: F401
                     PagePool)

@@ -1,87 +1,85 @@
-"""Host-side bookkeeping of the cache: page pools, per-request block lists, state slots.
+"""The cache manager's host side: page pools, per-request block lists, state slots.
 
-Nothing in this file touches a device, so every decision about pages can be tested on a
-machine without a GPU.
+The bookkeeping is the host library's (core/cache.cpp: PagePool, CacheLayout, BlockAllocator); the
+classes here are its Python face, so that every decision about pages can be driven and tested from
+Python on a machine without a GPU.
 
-What the reference does (one request at a time): a pool of fixed-size pages with a LIFO
-free list, optional page cap, double-free detection (src/core/Allocator.cpp:60-122,
-src/device/cuda/CudaPagedTensor.cpp:232-267); growth by ceil(new_len / page_size) pages
-(:95-137, :555-576); everything returned when the request's session ends (:528-553,
-src/server/Session.cpp:552-563); one list of cache groups per model
-(`CacheGroupConfig`, src/server/Session.h:36-41, src/server/Model.cpp:106-111).
+What the reference does (one request at a time): a pool of fixed-size pages with a LIFO free list,
+optional page cap, double-free detection (src/core/Allocator.cpp:60-122,
+src/device/cuda/CudaPagedTensor.cpp:232-267); growth by ceil(new_len / page_size) pages (:95-137,
+:555-576); everything returned when the request's session ends (:528-553,
+src/server/Session.cpp:552-563); one list of cache groups per model (`CacheGroupConfig`,
+src/server/Session.h:36-41, src/server/Model.cpp:106-111).
 
-What is different here: the lowest free page goes out first (so that a prompt's pages tend to
-be a run); many requests live at once and share the pools; a request has one
-block list per *group* (all layers of a group use the same page ids), not one page table
-per tensor; pages of a group whose layers only look back `window` positions are given back
-as soon as the window has passed them; and every request also holds one *state slot*, a
-row index into per-request state of fixed size.
+What is different here: the lowest free page goes out first (so that a prompt's pages tend to be a
+run); many requests live at once and share the pools; a request has one block list per *group* (all
+layers of a group use the same page ids), not one page table per tensor; pages of a group whose
+layers only look back `window` positions are given back as soon as the window has passed them; and
+every request also holds one *state slot*, a row index into per-request state of fixed size.
+
+Request ids may be any hashable value here; the library knows them by integers.
 """
 from __future__ import annotations
 
 import dataclasses
-import heapq
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
-from ..parts.base import PagedKVSpec, StateSpec
+from .. import core
+from ..errors import CacheError, NoFreeSlot, OutOfPages  # noqa: F401  (re-exported)
+from ..parts.base import PagedKVSpec, StateSpec, cache_spec_json
 
 FREED = -1   # entry of a block list whose page has been given back (window has passed it)
 
 
-class OutOfPages(Exception):
-    """A group's pool cannot supply the pages a reservation needs.  Nothing was taken."""
+class RequestIds:
+    """Hashable request ids <-> the integers the library knows requests by."""
 
+    def __init__(self):
+        self._to_int: Dict[Hashable, int] = {}
+        self._to_rid: Dict[int, Hashable] = {}
+        self._next = 1
 
-class NoFreeSlot(Exception):
-    """Every state slot is held by a live request."""
+    def of(self, rid: Hashable) -> int:
+        i = self._to_int.get(rid)
+        if i is None:
+            i = self._next
+            self._next += 1
+            self._to_int[rid] = i
+            self._to_rid[i] = rid
+        return i
 
+    def rid(self, i: int) -> Hashable:
+        return self._to_rid[i]
 
-class CacheError(Exception):
-    """A misuse of the cache: unknown request, page freed twice, shrinking a request..."""
+    def known(self, rid: Hashable) -> bool:
+        return rid in self._to_int
+
+    def forget(self, rid: Hashable) -> None:
+        i = self._to_int.pop(rid, None)
+        if i is not None:
+            self._to_rid.pop(i, None)
 
 
 class PagePool:
     """Page ids 0..num_pages-1; the free page with the lowest id is handed out first (the
-    reference's pool is a LIFO list).  A fresh pool hands out 0, 1, 2, ..., and whenever the low
-    end of the pool is free again a request's pages follow one another in the cache: the
-    prompt attention kernel fetches such runs with one copy per tile.  With few pages (the
-    tests) a page just freed is still handed out again at once."""
+    reference's pool is a LIFO list).  A fresh pool hands out 0, 1, 2, ..., and whenever the low end
+    of the pool is free again a request's pages follow one another in the cache: the prompt
+    attention kernel fetches such runs with one copy per tile.  With few pages (the tests) a page
+    just freed is still handed out again at once."""
 
     def __init__(self, num_pages: int):
-        if num_pages <= 0:
-            raise CacheError("a page pool needs at least one page")
+        self._h = core.Handle("pool", core.call("global", None, "new_pool", num_pages=num_pages)["handle"])
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages))      # a heap (an ascending list is one)
-        self._held = [False] * num_pages
-        self.high_water = 0
 
-    @property
-    def free_pages(self) -> int:
-        return len(self._free)
-
-    @property
-    def used_pages(self) -> int:
-        return self.num_pages - len(self._free)
+    free_pages = property(lambda self: self._h.call("info")["free_pages"])
+    used_pages = property(lambda self: self._h.call("info")["used_pages"])
+    high_water = property(lambda self: self._h.call("info")["high_water"])
 
     def allocate(self, n: int) -> List[int]:
-        if n > len(self._free):
-            raise OutOfPages(f"need {n} pages, {len(self._free)} of {self.num_pages} free")
-        pages = [heapq.heappop(self._free) for _ in range(n)]
-        for p in pages:
-            self._held[p] = True
-        self.high_water = max(self.high_water, self.used_pages)
-        return pages
+        return self._h.call("allocate", n=n)
 
     def release(self, pages: Sequence[int]) -> None:
-        pages = list(pages)
-        for p in pages:
-            if not (0 <= p < self.num_pages):
-                raise CacheError(f"page {p} does not belong to this pool")
-            if not self._held[p]:
-                raise CacheError(f"page {p} freed twice")
-            self._held[p] = False
-        for p in pages:
-            heapq.heappush(self._free, p)
+        self._h.call("release", pages=[int(p) for p in pages])
 
 
 @dataclasses.dataclass
@@ -99,41 +97,38 @@ class CacheLayout:
     groups: List[CacheGroup]
     group_of_cache: Dict[int, Tuple[int, int]]     # cache entry -> (group, index inside group)
     state_of_cache: Dict[int, StateSpec]           # cache entry -> fixed-size state
+    specs: Sequence[object] = ()
 
     @classmethod
     def from_specs(cls, specs: Sequence[object], page_size: int) -> "CacheLayout":
-        if page_size <= 0 or page_size & (page_size - 1):
-            # the reference enforces a power of two as well (src/ir/MidIRMaterializer.cpp:48-49)
-            raise CacheError(f"page size must be a power of two, got {page_size}")
-        groups: List[CacheGroup] = []
-        group_of_cache: Dict[int, Tuple[int, int]] = {}
-        state_of_cache: Dict[int, StateSpec] = {}
-        for ci, spec in enumerate(specs):
-            if spec is None:
-                continue
-            if isinstance(spec, StateSpec):
-                state_of_cache[ci] = spec
-                continue
-            if not isinstance(spec, PagedKVSpec):
-                raise CacheError(f"cache entry {ci}: unknown cache spec {spec!r}")
-            for g in groups:
-                if g.spec == spec:
-                    group_of_cache[ci] = (g.index, len(g.caches))
-                    g.caches.append(ci)
-                    break
-            else:
-                g = CacheGroup(len(groups), spec, [ci])
-                groups.append(g)
-                group_of_cache[ci] = (g.index, 0)
-        return cls(page_size, groups, group_of_cache, state_of_cache)
+        for ci, s in enumerate(specs):
+            if s is not None and not isinstance(s, (PagedKVSpec, StateSpec)):
+                raise CacheError(f"cache entry {ci}: unknown cache spec {s!r}")
+        probe = core.Handle("allocator", core.call("global", None, "new_allocator", specs=[cache_spec_json(s) for s in specs],
+                                                   pages=1, page_size=page_size, max_requests=1)["handle"])
+        return cls._from_json(probe.call("layout"), specs)
+
+    @classmethod
+    def _from_json(cls, j, specs=()) -> "CacheLayout":
+        groups = [CacheGroup(g["index"], PagedKVSpec(g["n_kv_heads"], g["head_dim"], g["window"] or None), list(g["caches"]))
+                  for g in j["groups"]]
+        states = {}
+        for ci in j["state_caches"]:
+            states[ci] = specs[ci] if ci < len(specs) else StateSpec(())
+        return cls(j["page_size"], groups, {int(k): tuple(v) for k, v in j["group_of_cache"].items()}, states, tuple(specs))
 
 
-@dataclasses.dataclass
-class _Request:
-    slot: int
-    length: int                       # tokens whose keys/values are in the cache
-    blocks: List[List[int]]           # per group: page id per block index, FREED where given back
-    version: int = 0                  # changes whenever a block list changes (never reused)
+class _PoolView:
+    def __init__(self, alloc: "BlockAllocator", group: int):
+        self._alloc, self._group = alloc, group
+
+    def _info(self):
+        return self._alloc._h.call("pools")[self._group]
+
+    num_pages = property(lambda self: self._info()["num_pages"])
+    free_pages = property(lambda self: self._info()["free_pages"])
+    used_pages = property(lambda self: self._info()["used_pages"])
+    high_water = property(lambda self: self._info()["high_water"])
 
 
 class BlockAllocator:
@@ -146,137 +141,75 @@ class BlockAllocator:
       release(rid)            the request ended: everything it holds is given back
     """
 
-    def __init__(self, layout: CacheLayout, pages_per_group: Sequence[int], max_requests: int):
-        if len(pages_per_group) != len(layout.groups):
-            raise CacheError("one page count per cache group is needed")
-        self.layout = layout
-        self.page_size = layout.page_size
-        self.pools = [PagePool(n) for n in pages_per_group]
-        self.max_requests = max_requests
-        self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
-        self._requests: Dict[Hashable, _Request] = {}
-        self._stamp = 0
+    def __init__(self, layout: Optional[CacheLayout] = None, pages_per_group: Sequence[int] = (), max_requests: int = 4, *,
+                 _handle: Optional[core.Handle] = None, _ids: Optional[RequestIds] = None):
+        if _handle is None:
+            if len(pages_per_group) != len(layout.groups):
+                raise CacheError("one page count per cache group is needed")
+            _handle = core.Handle("allocator", core.call(
+                "global", None, "new_allocator", specs=[cache_spec_json(s) for s in layout.specs],
+                pages=list(pages_per_group), page_size=layout.page_size, max_requests=max_requests)["handle"])
+        self._h = _handle
+        self.ids = _ids or RequestIds()
+        info = self._h.call("info")
+        self.page_size, self.max_requests = info["page_size"], info["max_requests"]
+        self.layout = layout if layout is not None else CacheLayout._from_json(self._h.call("layout"))
+        self.pools = [_PoolView(self, g) for g in range(info["n_groups"])]
+
+    def _call(self, method: str, rid: Hashable, **kw):
+        if not self.ids.known(rid) and method != "admit":
+            if method == "contains":
+                return False
+            raise CacheError(f"request {rid!r} is not live")
+        try:
+            return self._h.call(method, rid=self.ids.of(rid), **kw)
+        except CacheError as e:
+            raise CacheError(str(e).replace(f"request {self.ids.of(rid)} ", f"request {rid!r} ")) from None
 
     # ---- queries ---------------------------------------------------------------------
     def __contains__(self, rid) -> bool:
-        return rid in self._requests
+        return self.ids.known(rid) and self._h.call("contains", rid=self.ids.of(rid))
 
     def live(self) -> List[Hashable]:
-        return list(self._requests)
-
-    def _get(self, rid) -> _Request:
-        try:
-            return self._requests[rid]
-        except KeyError:
-            raise CacheError(f"request {rid!r} is not live") from None
+        return [self.ids.rid(i) for i in self._h.call("live")]
 
     def slot(self, rid) -> int:
-        return self._get(rid).slot
+        return self._call("slot", rid)
 
     def length(self, rid) -> int:
-        return self._get(rid).length
+        return self._call("length", rid)
 
     def block_version(self, rid) -> int:
-        """A number that changes whenever any of the request's block lists changes; a request
-        that is released and admitted again under the same id gets a new one."""
-        return self._get(rid).version
+        return self._call("block_version", rid)
 
     def block_list(self, rid, group: int) -> List[int]:
-        return self._get(rid).blocks[group]
+        return self._call("block_list", rid, group=group)
 
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._h.call("free_slots")
 
     def free_pages(self, group: int = 0) -> int:
-        return self.pools[group].free_pages
-
-    def _first_needed_block(self, group: int, length: int) -> int:
-        """Blocks below this index hold only positions no later query of a request of
-        `length` tokens will read."""
-        window = self.layout.groups[group].spec.window
-        if not window:
-            return 0
-        first_pos = max(0, length - window + 1)   # oldest key the next query (position `length`) reads
-        return first_pos // self.page_size
+        return self._h.call("free_pages", group=group)
 
     def pages_needed(self, rid, new_len: int) -> List[int]:
-        """Pages each group would have to supply for reserve(rid, new_len)."""
-        r = self._get(rid)
-        want_blocks = -(-new_len // self.page_size)
-        return [max(0, want_blocks - len(bl)) for bl in r.blocks]
-
-    def pages_for_new_request(self, n_tokens: int) -> List[int]:
-        return [-(-n_tokens // self.page_size)] * len(self.pools)
+        return self._call("pages_needed", rid, new_len=new_len)
 
     def can_reserve(self, rid, new_len: int) -> bool:
-        return all(n <= p.free_pages for n, p in zip(self.pages_needed(rid, new_len), self.pools))
+        return self._call("can_reserve", rid, new_len=new_len)
 
     # ---- transitions -----------------------------------------------------------------
     def admit(self, rid) -> int:
-        if rid in self._requests:
-            raise CacheError(f"request {rid!r} is already live")
-        if not self._free_slots:
-            raise NoFreeSlot(f"all {self.max_requests} state slots are in use")
-        slot = self._free_slots.pop()
-        self._stamp += 1
-        self._requests[rid] = _Request(slot, 0, [[] for _ in self.pools], self._stamp)
-        return slot
+        return self._call("admit", rid)
 
     def reserve(self, rid, new_len: int) -> None:
-        r = self._get(rid)
-        if new_len < r.length:
-            raise CacheError(f"request {rid!r} holds {r.length} tokens, cannot reserve for {new_len}")
-        need = self.pages_needed(rid, new_len)
-        for g, (n, pool) in enumerate(zip(need, self.pools)):
-            if n > pool.free_pages:
-                raise OutOfPages(f"group {g}: request {rid!r} needs {n} more pages for {new_len} tokens, "
-                                 f"{pool.free_pages} of {pool.num_pages} free")
-        for bl, n, pool in zip(r.blocks, need, self.pools):
-            if n:
-                bl.extend(pool.allocate(n))
-                self._stamp += 1
-                r.version = self._stamp
+        self._call("reserve", rid, new_len=new_len)
 
     def commit(self, rid, new_len: int) -> None:
-        r = self._get(rid)
-        if new_len < r.length:
-            raise CacheError(f"request {rid!r} cannot shrink from {r.length} to {new_len}")
-        cap = min((len(bl) for bl in r.blocks), default=None)
-        if cap is not None and new_len > cap * self.page_size:
-            raise CacheError(f"request {rid!r}: {new_len} tokens were not reserved")
-        r.length = new_len
-        for g, bl in enumerate(r.blocks):
-            first = min(self._first_needed_block(g, new_len), len(bl))
-            gone = [p for p in bl[:first] if p != FREED]
-            if gone:
-                self.pools[g].release(gone)
-                for i in range(first):
-                    bl[i] = FREED
-                self._stamp += 1
-                r.version = self._stamp
+        self._call("commit", rid, new_len=new_len)
 
     def release(self, rid) -> None:
-        r = self._get(rid)
-        for bl, pool in zip(r.blocks, self.pools):
-            pool.release([p for p in bl if p != FREED])
-        self._free_slots.append(r.slot)
-        del self._requests[rid]
+        self._call("release", rid)
 
-    # ---- self-check (tests call this after every operation) ---------------------------
     def check(self) -> None:
         """No page lost, held twice or free while held; no slot lost or shared."""
-        for g, pool in enumerate(self.pools):
-            held = [p for r in self._requests.values() for p in r.blocks[g] if p != FREED]
-            if len(held) != len(set(held)):
-                raise CacheError(f"group {g}: a page is held twice")
-            free = pool._free
-            if len(free) != len(set(free)):
-                raise CacheError(f"group {g}: a page is on the free list twice")
-            if set(held) & set(free):
-                raise CacheError(f"group {g}: a held page is on the free list")
-            if len(held) + len(free) != pool.num_pages:
-                raise CacheError(f"group {g}: {pool.num_pages - len(held) - len(free)} pages lost")
-        slots = [r.slot for r in self._requests.values()]
-        if len(slots) != len(set(slots)) or set(slots) & set(self._free_slots) \
-                or len(slots) + len(self._free_slots) != self.max_requests:
-            raise CacheError("state slots are inconsistent")
+        self._h.call("check")

@@ -301,6 +301,9 @@ struct Parser {
         } else if (c == 't') { expect("true"); out = Json(true); }
         else if (c == 'f') { expect("false"); out = Json(false); }
         else if (c == 'n') { expect("null"); }
+        else if (c == 'N') { expect("NaN"); out = Json(std::nan("")); }              // as Python's json module writes them
+        else if (c == 'I') { expect("Infinity"); out = Json((double)INFINITY); }
+        else if (c == '-' && text.compare(pos, 9, "-Infinity") == 0) { pos += 9; out = Json(-(double)INFINITY); }
         else if (c == '-' || (c >= '0' && c <= '9')) out = number();
         else fail(std::string("unexpected character '") + c + "'");
         depth--;

@@ -168,6 +168,117 @@ def load_library(name: str) -> ctypes.CDLL:
         return lib
 
 
+# ---- the host library (sandyrt_b200/core/*.cpp -> libsandy_core.so) ---------------------------------
+CORE_DIR = os.path.join(os.path.dirname(CSRC_DIR), "core")
+CORE_NAME = "libsandy_core"
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-fvisibility-inlines-hidden", "-Wall",
+             "-Wno-unused-function"]
+# -Bsymbolic: the library binds its own template instantiations (std::regex and the like) instead of
+# same-named ones another library of the process may export (torch does, built against another ABI).
+LINK_FLAGS = ["-Wl,-Bsymbolic"]
+
+
+def _core_sources() -> List[str]:
+    return sorted(f for f in os.listdir(CORE_DIR) if f.endswith(".cpp"))
+
+
+def _core_hash() -> str:
+    h = hashlib.sha256()
+    names = sorted(f for f in os.listdir(CORE_DIR) if f.endswith((".cpp", ".h"))) 
+    for fname in names:
+        with open(os.path.join(CORE_DIR, fname), "rb") as f:
+            h.update(fname.encode())
+            h.update(f.read())
+    with open(os.path.join(CSRC_DIR, "sandy_kernels.h"), "rb") as f:
+        h.update(f.read())
+    h.update(" ".join(CXX_FLAGS + LINK_FLAGS).encode())
+    return h.hexdigest()
+
+
+def core_library_path() -> str:
+    return os.path.join(_build_dir(), CORE_NAME + ".so")
+
+
+def core_is_current() -> bool:
+    so = core_library_path()
+    stamp = so + ".stamp"
+    if not (os.path.isfile(so) and os.path.isfile(stamp)):
+        return False
+    with open(stamp) as f:
+        return f.read().strip() == _core_hash()
+
+
+def compile_core(verbose: bool = True) -> str:
+    """Build the host library: every core/*.cpp with the C++ compiler (in parallel), linked against
+    the CUDA runtime.  No device code is in it; the kernels stay in their own libraries."""
+    nvcc = _find_nvcc()
+    cuda_home = os.path.dirname(os.path.dirname(os.path.realpath(nvcc)))
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise KernelBuildError("no C++ compiler found (looked at $CXX, g++, c++); the host library cannot be built")
+    so = core_library_path()
+    objdir = os.path.join(_build_dir(), f"core_obj_{os.getpid()}")
+    os.makedirs(objdir, exist_ok=True)
+    t0 = time.time()
+    if verbose:
+        print(f"[sandyrt_b200] compiling the host library ({len(_core_sources())} files) ...", file=sys.stderr, flush=True)
+    errors: List[str] = []
+    objects: List[str] = []
+
+    def work(src):
+        obj = os.path.join(objdir, src[:-4] + ".o")
+        objects.append(obj)
+        cmd = [cxx] + CXX_FLAGS + ["-I", os.path.join(cuda_home, "include"), "-c", os.path.join(CORE_DIR, src), "-o", obj]
+        res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, cwd=CORE_DIR)
+        if res.returncode != 0:
+            errors.append(f"{src}:\n" + res.stdout.decode("utf-8", "replace"))
+
+    threads = [threading.Thread(target=work, args=(s,)) for s in _core_sources()]
+    for t in threads:
+        t.start()
+    while any(t.is_alive() for t in threads):
+        for t in threads:
+            t.join(timeout=5.0 / max(1, len(threads)))
+        if verbose and time.time() - t0 > 5 and int(time.time() - t0) % 5 == 0:
+            print(f"[sandyrt_b200]   still compiling the host library ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+            time.sleep(1.0)
+    try:
+        if errors:
+            raise KernelBuildError("the host library failed to compile:\n" + "\n".join(errors))
+        tmp = f"{so}.{os.getpid()}.tmp"
+        libdir = os.path.join(cuda_home, "lib64")
+        cmd = [cxx, "-shared"] + LINK_FLAGS + ["-o", tmp] + sorted(objects) + ["-L", libdir, "-lcudart_static", "-lrt", "-lpthread", "-ldl"]
+        res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        if res.returncode != 0:
+            raise KernelBuildError("the host library failed to link:\n" + res.stdout.decode("utf-8", "replace"))
+        os.replace(tmp, so)
+        with open(so + ".stamp", "w") as f:
+            f.write(_core_hash())
+    finally:
+        shutil.rmtree(objdir, ignore_errors=True)
+    if verbose:
+        print(f"[sandyrt_b200] built {CORE_NAME}.so in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    return so
+
+
+_core: Optional[ctypes.CDLL] = None
+
+
+def load_core() -> ctypes.CDLL:
+    """The loaded host library, building it first if it is missing or stale."""
+    global _core
+    with _lock:
+        if _core is not None:
+            return _core
+        if not core_is_current():
+            compile_core()
+        try:
+            _core = ctypes.CDLL(core_library_path())
+        except OSError as e:
+            raise KernelBuildError(f"cannot load {core_library_path()}: {e}") from e
+        return _core
+
+
 def build_all(verbose: bool = True, names: Optional[List[str]] = None) -> List[str]:
     """Build every library that is missing or stale (in parallel); return their paths."""
     names = [n for n in (names or list(LIBRARIES)) if os.path.isfile(os.path.join(CSRC_DIR, n + ".cu"))]
@@ -187,4 +298,8 @@ def build_all(verbose: bool = True, names: Optional[List[str]] = None) -> List[s
         t.join()
     if errors:
         raise KernelBuildError("\n".join(errors))
-    return [library_path(n) for n in names]
+    out = [library_path(n) for n in names]
+    if not core_is_current():
+        compile_core(verbose)
+    out.append(core_library_path())
+    return out

@@ -1,19 +1,22 @@
-"""Python face of the CUDA kernels: argument checks, then one ctypes call per launch.
+"""Python face of the CUDA kernels, one function per kernel: argument checks, then one ctypes call
+per launch.  The kernel tests and the micro-benchmarks call kernels by name through it; the engine
+itself launches the same kernels from the host library (core/ops.cpp), which also holds the choice
+among kernels that serve one operation.
 
-Every function works on torch CUDA tensors, launches on torch's current stream (so a
-launch can be captured in a CUDA graph) and returns nothing; outputs are written into
-tensors the caller passes.  Sizes a kernel does not take are refused with UnsupportedShape
-before anything runs.  There is no other implementation behind these functions: if the
-library cannot be built or loaded, the call raises.
+Every function works on torch CUDA tensors, launches on torch's current stream and returns nothing;
+outputs are written into tensors the caller passes.  Sizes a kernel does not take are refused with
+UnsupportedShape before anything runs.  There is no other implementation behind these functions:
+if the library cannot be built or loaded, the call raises.
 """
 from __future__ import annotations
 
 import ctypes
-import os
+import dataclasses
 from typing import Optional
 
 import torch
 
+from ..errors import KernelError, UnsupportedShape  # noqa: F401  (re-exported)
 from .build import load_library
 
 F32, BF16 = 0, 1
@@ -22,12 +25,27 @@ SKINNY_MAX_ROWS = 64
 ACT_CODES = {None: 0, "none": 0, "gelu_new": 1, "gelu_tanh": 1, "gelu": 2, "gelu_erf": 2}
 
 
-class KernelError(RuntimeError):
-    pass
+@dataclasses.dataclass
+class FusedNorm:
+    """A LayerNorm that gemm_skinny runs itself on the float32 rows `x`."""
+    x: torch.Tensor
+    gamma: torch.Tensor
+    beta: Optional[torch.Tensor]
+    eps: float
 
 
-class UnsupportedShape(KernelError):
-    pass
+@dataclasses.dataclass
+class KVTarget:
+    """Where the key/value columns of a fused q/k/v product belong: a layer's cache views
+    [num_pages, Hkv, page_size, D] and the step's index arrays."""
+    k_cache: torch.Tensor
+    v_cache: torch.Tensor
+    block_table: torch.Tensor
+    token_seq: torch.Tensor
+    positions: torch.Tensor
+    q_cols: int
+    kv_cols: int
+    head_dim: int
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -196,51 +214,16 @@ def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out,
 _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16, 32, 64, 128)}
 
 
-_FORCED_SPLITS = int(os.environ.get("SANDYRT_DECODE_SPLITS", "0"))      # > 0: this many splits, for comparisons
-
-
-_SM_COUNT = 0
-
-
-def sm_count() -> int:
-    """Streaming multiprocessors of the current device (asked once)."""
-    global _SM_COUNT
-    if _SM_COUNT == 0:
-        _SM_COUNT = int(load_library("embed").sandy_device_sm_count())
-    return _SM_COUNT
-
-
-def spin(nanoseconds: int) -> None:
-    """Keep the current stream busy for about this long (timing loops queue their launches behind it)."""
-    code = load_library("embed").sandy_spin(ctypes.c_longlong(int(nanoseconds)), _stream())
-    if code:
-        raise KernelError(f"spin: CUDA error {code}")
-
-
 def decode_splits(n_tokens: int, n_heads: int, max_kv: int, sms: Optional[int] = None) -> int:
-    """How many blocks share the keys of one (token, head) pair: enough to fill the GPU's
-    SMs a few times over, but no block with fewer than 64 keys.  It depends on the launch
-    shape only (not on the requests' exact lengths), so a recorded graph stays valid."""
-    if _FORCED_SPLITS:
-        return _FORCED_SPLITS
-    want = -(-4 * (sms or sm_count()) // max(1, n_tokens * n_heads))
-    cap = max(1, max_kv // 64)
-    n = max(1, min(want, cap, 32))
-    # The splits of a pair are one thread-block cluster.  Clusters of 6 and 7 blocks pack badly into
-    # the GPU's groups of SMs: a whole decode step of 8 x 12 pairs took 0.439 / 0.441 ms with them
-    # against 0.376 ms with 5 (0.383 with 4, 0.420 with 8).
-    return 5 if n in (6, 7) else n
+    """How many blocks share the keys of one (token, head) pair in a decode step (the host library's
+    rule, core/ops.cpp): enough to fill the GPU's SMs a few times over, but no block with fewer than
+    64 keys, and never a cluster of 6 or 7 blocks."""
+    from .. import core
 
+    return core.call("global", None, "decode_splits", n_tokens=n_tokens, n_heads=n_heads, max_kv=max_kv, sms=sms or 0)
 
 
 CLUSTER_MAX_SPLITS = 8
-# From this many (token, head) pairs on, a decode step's attention streams pages through shared
-# memory with bulk copies (attention_decode_bulk.cu) instead of through registers.  Measured on
-# GPT-2 small's shape: 64 x 12 pairs of 384 keys, cache read from HBM, 18.8 against 45.5 us a
-# layer; but a whole decode step of 8 x 12 pairs (its cache fits in L2) took 414 against 400 us
-# and one of 1 x 12 pairs 356 against 333 us, the register kernel starting sooner.
-BULK_MIN_PAIRS = 256
-_BULK_MODE = os.environ.get("SANDYRT_DECODE_BULK", "auto")     # "0" / "1" force one kernel, for comparisons
 
 
 def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int,
@@ -304,10 +287,6 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
         LAUNCHES += 1
 
 
-# Heads of 64 go to the tcgen05 kernel; "0" keeps every head size on the mma.sync kernel (for comparisons).
-_PREFILL_TC = os.environ.get("SANDYRT_PREFILL_TC", "1") != "0"
-
-
 def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out, *, n_heads: int,
                       max_q_len: int, scale: float, window: int = 0, tc=None) -> None:
     """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).
@@ -332,7 +311,7 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
             ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len), ctypes.c_int(n_heads),
             ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
             ctypes.c_int(num_pages), _p(kernel_status(q.device)), _stream())
-    if tc or (tc is None and _PREFILL_TC and d == 64):
+    if tc or (tc is None and d == 64):
         code = load_library("attention_prefill_tc").sandy_prefill_attention_tc(*args)
         if code != -1 or tc:
             _check(code, f"prefill_attention_tc(H={n_heads},Hkv={hkv},D={d})")
@@ -346,26 +325,6 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
                                        ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_pages),
                                        _p(kernel_status(q.device)), _stream())
     _check(code, f"prefill_attention(H={n_heads},Hkv={hkv},D={d})")
-
-
-def attention(ctx, q, k_cache, v_cache, block_table, out, *, n_heads: int, scale: float, window: int = 0) -> None:
-    """Attention of a step's tokens over the cache: picks the kernel for the step's shape."""
-    d = k_cache.shape[3]
-    if ctx.max_q_len > 1 and q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 128:
-        prefill_attention(q, k_cache, v_cache, block_table, ctx.q_start, ctx.kv_before, out, n_heads=n_heads,
-                          max_q_len=ctx.max_q_len, scale=scale, window=window)
-        return
-    if ctx.max_q_len == 1 and d in _DECODE_HEAD_DIMS.get(q.dtype, ()):
-        max_kv = block_table.shape[1] * k_cache.shape[2]
-        splits = min(decode_splits(ctx.n_tokens, n_heads, max_kv), CLUSTER_MAX_SPLITS)
-        stage = 2 * k_cache.shape[2] * d * q.element_size()
-        fits = stage * 4 <= 160 * 1024          # the ring holds at least four stages
-        bulk = fits and (ctx.n_tokens * n_heads >= BULK_MIN_PAIRS if _BULK_MODE == "auto" else _BULK_MODE == "1")
-        decode_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out, n_heads=n_heads,
-                         scale=scale, window=window, num_splits=splits, cluster=True, bulk=bulk)
-        return
-    paged_attention(q, k_cache, v_cache, block_table, ctx.token_seq, ctx.positions, out,
-                    n_heads=n_heads, scale=scale, window=window)
 
 
 def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, uniform=None, status=None,
@@ -482,96 +441,32 @@ def gemm_tc(a, w, bias, out, *, act=None, residual=None, tile_n: int = 0, kv=Non
                   _p(kernel_status(a.device)), _stream())
         _check(code, f"gemm_tc(M={M},N={N},K={K},tile={tile},kv={kv is not None})")
 
-    if tile_n == 0 and M >= GEMM_TUNE_MIN_ROWS:
-        tile_n = _tuned_tile(launch, a, out, residual, M, N, K, act)
-    elif tile_n == 0:
-        tile_n = _gemm_tiles.get((-(-M // 128), N, K, ACT_CODES[act], residual is not None, out.dtype,
-                                  a.device.index), 0)
-    launch(tile_n, out, residual)
+    launch(tile_n, out, residual)         # tile_n 0: the kernel's own choice
 
 
-# Which of the tcgen05 variants (three tile widths, one tile per CTA or persistent; two CTAs on a
-# 256-row tile, two widths) is fastest
-# depends on how the tiles of a product fall on the SMs, and a model of it was off by 20 % on
-# half the shapes tried.  So the first product of a shape (rows in steps of 128) with at least
-# this many rows times each variant on a scratch output and remembers the winner.  All variants
-# add the k-steps of an output element in the same order, so the choice never changes a result.
-# Not done while a CUDA graph is being captured (the kernel's own default stands then).
-GEMM_TUNE_MIN_ROWS = 256
-PAIR_TILE = 2000          # tile_n = PAIR_TILE + 128 or + 256: the two-CTA kernel (gemm_tc2.cu)
+# The tcgen05 variants (three tile widths, one tile per CTA or persistent; two CTAs on a 256-row
+# tile, two widths), as `tile_n` codes: n > 0 one tile of 128 x n per CTA, n < 0 the persistent
+# kernel, PAIR_TILE + n the two-CTA kernel (gemm_tc2.cu).  The engine times them on the first
+# product of a shape and keeps the winner (core/ops.cpp).
+PAIR_TILE = 2000
 GEMM_VARIANTS = (-64, -128, -256, 64, 128, 256, PAIR_TILE + 128, PAIR_TILE + 256)
-_gemm_tiles: dict = {}
-
-
-TUNE_LAUNCHES = 8
-
-
-def _time_queued(fn) -> float:
-    """Device milliseconds of TUNE_LAUNCHES calls of fn, run back to back.  A launch costs the host
-    about as long as one of these kernels takes the GPU, so timed naively the host's pace is what is
-    measured; here the GPU is kept busy with a spin kernel while the launches queue up behind it."""
-    fn()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    spin(300_000)                            # 0.3 ms: the launches below are all queued before it ends
-    e0.record()
-    for _ in range(TUNE_LAUNCHES):
-        fn()
-    e1.record()
-    e1.synchronize()
-    return e0.elapsed_time(e1)
-
-
-def _tuned_tile(launch, a, out, residual, M: int, N: int, K: int, act) -> int:
-    key = (-(-M // 128), N, K, ACT_CODES[act], residual is not None, out.dtype, a.device.index)
-    hit = _gemm_tiles.get(key)
-    if hit is not None:
-        return hit
-    if torch.cuda.is_current_stream_capturing():
-        return 0
-    scratch = torch.empty_like(out)
-    best, best_us = 0, float("inf")
-    for tile in GEMM_VARIANTS:               # timed without the cache write: the scratch runs must not touch pages
-        us = _time_queued(lambda: launch(tile, scratch, residual, False))
-        if us < best_us:
-            best, best_us = tile, us
-    _gemm_tiles[key] = best
-    return best
 
 
 SKINNY_NORM_MAX_ROWS = 16
 SKINNY_NORM_MAX_K = 2048
 
-# Between 17 and 64 rows neither kernel always wins (measured at 64 rows on GPT-2 small: the
-# up-projection, 3,072 columns, 5.9 us on tcgen05 against 10.7 us skinny; the out-projection, 768
-# columns, 6.1 against 4.2: a 128 x 64 tile per CTA leaves most SMs idle when there are few
-# columns).  The two kernels add in different orders, so the choice is a fixed rule of the shape
-# and never a timing: the same batch gives the same bfloat16 tokens in every process.
-SMALL_TC_MIN_ROWS = 33
-SMALL_TC_MIN_COLS = 2048
-
-
-def small_gemm_prefers_tc(M: int, N: int, K: int) -> bool:
-    """Whether a 17..64-row product with nothing fused into it goes to the tcgen05 kernel (one
-    128 x 64 tile per CTA) instead of the skinny one."""
-    return M >= SMALL_TC_MIN_ROWS and N >= SMALL_TC_MIN_COLS and tensor_core_gemm_supported(K, N)
-
-
-def skinny_norm_fusable(lazy, K: int) -> bool:
-    """Whether gemm_skinny can run this LazyNorm inside itself: a LayerNorm with bfloat16
-    gain/offset, at most 16 rows, K at most 2048 (the row is held in registers)."""
-    norm = lazy.norm
-    gamma = getattr(norm, "gamma", None)
-    return (getattr(norm, "fusable_kind", None) == "layernorm" and gamma is not None
-            and gamma.dtype == torch.bfloat16 and lazy.out_dtype == torch.bfloat16
-            and lazy.x.dtype == torch.float32 and lazy.x.shape[0] <= SKINNY_NORM_MAX_ROWS
-            and K <= SKINNY_NORM_MAX_K and lazy.x.stride(1) == 1 and lazy.x.stride(0) % 4 == 0
-            and lazy.x.data_ptr() % 16 == 0 and gamma.data_ptr() % 16 == 0
-            and (getattr(norm, "beta", None) is None or norm.beta.data_ptr() % 16 == 0))
+def skinny_norm_fusable(norm: FusedNorm, K: int) -> bool:
+    """Whether gemm_skinny can run this LayerNorm inside itself: bfloat16 gain/offset, at most 16
+    rows, K at most 2048 (the row is held in registers)."""
+    return (norm.gamma.dtype == torch.bfloat16 and norm.x.dtype == torch.float32
+            and norm.x.shape[0] <= SKINNY_NORM_MAX_ROWS and K <= SKINNY_NORM_MAX_K and norm.x.stride(1) == 1
+            and norm.x.stride(0) % 4 == 0 and norm.x.data_ptr() % 16 == 0 and norm.gamma.data_ptr() % 16 == 0
+            and (norm.beta is None or norm.beta.data_ptr() % 16 == 0))
 
 
 def gemm_skinny(a, w, bias, out, *, act=None, residual=None, norm=None, kv=None) -> None:
     """out = act(a @ w.T + bias) + residual for up to 64 rows (a decode step), weight-streaming.
-    Same operand rules as gemm_tc.  With `norm` (a LazyNorm that skinny_norm_fusable accepted)
+    Same operand rules as gemm_tc.  With `norm` (a FusedNorm that skinny_norm_fusable accepted)
     `a` is None and the LayerNorm of norm.x runs inside the kernel.  With `kv` (a KVTarget) the
     key and value columns of the product are also written into the cache pages."""
     M, K = (norm.x.shape if norm is not None else a.shape)
@@ -579,7 +474,7 @@ def gemm_skinny(a, w, bias, out, *, act=None, residual=None, norm=None, kv=None)
     x = gamma = beta = None
     eps = 0.0
     if norm is not None:
-        x, gamma, beta, eps = norm.x, norm.norm.gamma, norm.norm.beta, float(norm.norm.eps)
+        x, gamma, beta, eps = norm.x, norm.gamma, norm.beta, float(norm.eps)
         if not skinny_norm_fusable(norm, K):
             raise UnsupportedShape("gemm_skinny: this norm cannot be fused")
     elif a.dtype != torch.bfloat16:

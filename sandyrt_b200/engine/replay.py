@@ -1,7 +1,8 @@
 """Trace replay: feed given token ids through a model step by step and write the logits.
 
-It samples nothing.  It drives the same Model, Engine.step, cache manager and kernels that
-generation uses; nothing here computes anything about the model itself.
+It samples nothing.  It drives the same model, step function, cache manager and kernels that
+generation uses (the host library's, through Engine.step); nothing here computes anything about
+the model itself.
 
 Input, one JSON object per line:
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": ["b"]}
@@ -66,8 +67,6 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, lines,
                 tmp = os.path.join(out_dir, f"{step}.f32.tmp")
                 host.tofile(tmp)
                 os.replace(tmp, os.path.join(out_dir, f"{step}.f32"))
-            else:
-                torch.cuda.current_stream().synchronize()
             engine.check_status()
         for rid in rec.get("end", []):
             if rid in engine.cache.alloc:

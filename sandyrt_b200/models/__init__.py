@@ -1,5 +1,3 @@
-"""Architectures shipped with the engine.  Importing this package registers them.
-(The Model class lives in `models.model`; it is not imported here so that the parts,
-which the model is built from, can import the spec types without a cycle.)"""
-from . import gpt2  # noqa: F401
+"""Model descriptions and the Model handle.  The architectures shipped with the engine (GPT-2) are
+described by the host library (core/config.cpp, describe_gpt2)."""
 from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec  # noqa: F401

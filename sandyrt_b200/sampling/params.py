@@ -8,12 +8,15 @@ temperature >= 0 and finite.  temperature 0 is greedy.
 One difference: the reference's default top_k = 1 makes every draw greedy until a model's
 model_config.json raises it (src/server/Model.cpp:63-96).  Here top_k = 0 means "no top-k
 cut" and is the default, so `temperature` alone switches sampling on.
+
+The checks are the host library's (core/sampling.h).
 """
 from __future__ import annotations
 
 import dataclasses
-import math
 from typing import Optional
+
+from .. import core
 
 
 @dataclasses.dataclass(frozen=True)
@@ -24,12 +27,8 @@ class SamplingParams:
     seed: Optional[int] = None  # None: a fresh seed per request
 
     def validate(self) -> "SamplingParams":
-        if self.top_k < 0:
-            raise ValueError("top_k must be >= 0 (0 keeps the whole vocabulary)")
-        if not math.isfinite(self.top_p) or self.top_p <= 0.0 or self.top_p > 1.0:
-            raise ValueError("top_p must be > 0 and <= 1")
-        if not math.isfinite(self.temperature) or self.temperature < 0.0:
-            raise ValueError("temperature must be >= 0")
+        core.call("global", None, "validate_sampling", temperature=float(self.temperature), top_k=int(self.top_k),
+                  top_p=float(self.top_p))
         return self
 
     @property

@@ -509,16 +509,11 @@ def test_gemm_skinny(M, N, K):
 def test_gemm_skinny_with_the_norm_inside(M, K, N, eps):
     """LayerNorm run inside the product equals the stand-alone norm kernel followed by the product."""
     from sandyrt_b200.csrc import ops
-    from sandyrt_b200.parts.linear import LazyNorm
 
-    class N_:                                    # the fields of a LayerNorm part the kernel reads
-        fusable_kind = "layernorm"
-    norm = N_()
-    norm.gamma, norm.beta, norm.eps = _rand((K,), torch.bfloat16, 4) + 1.0, _rand((K,), torch.bfloat16, 5), eps
     x = _rand((M, K), torch.float32, 1, scale=2.0) + 0.3
+    norm = lazy = ops.FusedNorm(x, _rand((K,), torch.bfloat16, 4) + 1.0, _rand((K,), torch.bfloat16, 5), eps)
     w = _rand((N, K), torch.bfloat16, 2, scale=0.1)
     bias = _rand((N,), torch.bfloat16, 3)
-    lazy = LazyNorm(None, norm, x, torch.bfloat16)
     assert ops.skinny_norm_fusable(lazy, K)
     got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
     ops.gemm_skinny(None, w, bias, got, act="gelu_new", norm=lazy)
@@ -538,7 +533,7 @@ def test_gemm_skinny_with_the_norm_inside(M, K, N, eps):
 def test_gemm_skinny_writes_keys_and_values_into_the_pages():
     """The fused q/k/v product puts its key and value columns where kv_append would."""
     from sandyrt_b200.csrc import ops
-    from sandyrt_b200.parts.linear import KVTarget
+    from sandyrt_b200.csrc.ops import KVTarget
 
     H, Hkv, D, ps = 6, 2, 32, 8
     q_cols, kv_cols = H * D, Hkv * D
@@ -583,7 +578,7 @@ def test_gemm_tc_writes_keys_and_values_into_the_pages(tile_n, H, Hkv, D, ps):
     (one behind a prefix, tokens that cross page edges), column ranges that are no multiple of
     the kernel's 32-column chunks."""
     from sandyrt_b200.csrc import ops
-    from sandyrt_b200.parts.linear import KVTarget
+    from sandyrt_b200.csrc.ops import KVTarget
 
     q_cols, kv_cols = H * D, Hkv * D
     K = 96

@@ -26,92 +26,61 @@ def _spec(kind, params, names):
     return PartSpec(kind, params, {n: n for n in names})
 
 
-def _random_bind(part, seed, dtype):
-    from sandyrt_b200.weights.random_init import random_tensors
+def _harness(family, spec, dtype, **kw):
+    """The host library's part of this description, alone: bound to seeded random tensors, with a
+    poisoned cache of its own."""
+    from sandyrt_b200.parts.harness import PartHarness
 
-    tensors = random_tensors(part.requests(), seed, torch.float32)
-    part.bind(tensors, DEV, dtype)
-    return {k: v.numpy() for k, v in tensors.items()}
-
-
-def _ctx(cache_specs, seqs, dtype, page_size=8):
-    """A hand-made StepContext for parts run outside a model.  seqs: [(kv_before, q_len)]."""
-    from sandyrt_b200.cache.manager import CacheManager
-    from sandyrt_b200.parts.base import StepContext, Workspace
-
-    cm = CacheManager(cache_specs, page_size=page_size, max_tokens=512, max_requests=8, device=DEV, dtype=dtype)
-    cm.device_caches.poison()
-    pos, seq, qs = [], [], [0]
-    for s, (before, n) in enumerate(seqs):
-        cm.admit(s)
-        cm.alloc.reserve(s, before + n)
-        pos += list(range(before, before + n)); seq += [s] * n; qs.append(qs[-1] + n)
-    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    max_blocks = max(len(cm.alloc.block_list(s, 0)) for s in range(len(seqs))) if cm.layout.groups else 1
-    tables = {}
-    for g in cm.layout.groups:
-        t = torch.full((len(seqs), max_blocks), -1, dtype=torch.int32)
-        for s in range(len(seqs)):
-            bl = cm.alloc.block_list(s, g.index)
-            t[s, :len(bl)] = torch.tensor(bl, dtype=torch.int32)
-        tables[g.index] = t.to(DEV)
-    T = len(pos)
-    return StepContext(
-        n_tokens=T, n_seqs=len(seqs), token_ids=i32([0] * T), positions=i32(pos), token_seq=i32(seq),
-        seq_slots=i32([cm.alloc.slot(s) for s in range(len(seqs))]), q_start=i32(qs),
-        kv_before=i32([b for b, _ in seqs]), logit_rows=i32([]), block_tables=tables, compute_dtype=dtype,
-        workspace=Workspace(DEV), caches=cm.device_caches, host_q_lens=[n for _, n in seqs],
-        host_kv_before=[b for b, _ in seqs], host_slots=[cm.alloc.slot(s) for s in range(len(seqs))],
-        max_q_len=max(n for _, n in seqs), max_kv_len=max(b + n for b, n in seqs)), cm
+    return PartHarness(family, spec, dtype, **kw)
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
 def test_layernorm_part(dtype, tol):
-    from sandyrt_b200.registry import get_part
-
-    part = get_part("norm", "layernorm")(_spec("layernorm", {"width": 96, "eps": 1e-6}, ["weight", "bias"]))
-    w = _random_bind(part, 1, dtype)
+    part = _harness("norm", _spec("layernorm", {"width": 96, "eps": 1e-6}, ["weight", "bias"]), dtype, seed=1)
+    w = part.tensors()
     x = torch.randn(11, 96, device=DEV) * 2 + 0.5
     out = torch.empty(11, 96, dtype=dtype, device=DEV)
-    part.forward(None, x, out)
-    want = plain.layer_norm(_np(x), w["weight"], w["bias"], 1e-6)
+    part.run_norm(x, out)
+    rnd = plain.round_bf16 if dtype == torch.bfloat16 else (lambda a: a)
+    want = plain.layer_norm(_np(x), rnd(w["weight"]), rnd(w["bias"]), 1e-6)
     assert np.abs(_np(out) - want).max() < tol
+    # selected rows only (what the final norm does with the wanted rows)
+    some = torch.empty(3, 96, dtype=dtype, device=DEV)
+    part.run_norm(x, some, rows=[7, 0, 10])
+    assert np.abs(_np(some) - want[[7, 0, 10]]).max() < tol
 
 
 def test_embedding_with_learned_positions():
-    from sandyrt_b200.parts.base import StepContext, Workspace
-    from sandyrt_b200.parts.embedding import TokenEmbedding
-    from sandyrt_b200.registry import get_part
-
-    emb = TokenEmbedding(_spec("token_embedding", {"vocab_size": 77, "width": 48}, ["weight"]))
-    pos = get_part("position", "learned_absolute")(_spec("learned_absolute", {"width": 48, "max_positions": 20}, ["weight"]))
-    we, wp = _random_bind(emb, 1, torch.float32), _random_bind(pos, 2, torch.float32)
-    ctx, _ = _ctx([], [(3, 4), (0, 2)], torch.float32)
+    emb = _harness("embedding", _spec("token_embedding", {"vocab_size": 77, "width": 48}, ["weight"]), torch.float32,
+                   position=_spec("learned_absolute", {"width": 48, "max_positions": 20}, ["weight"]), seed=1)
+    we, wp = emb.tensors(), emb.position_tensors()
     ids = [5, 76, 0, 13, 9, 9]
-    ctx.token_ids = torch.tensor(ids, dtype=torch.int32, device=DEV)
-    ctx.position = pos
+    emb.set_step([(3, 4), (0, 2)], ids)
     x = torch.empty(6, 48, device=DEV)
-    emb.forward(ctx, x, None)
+    emb.run_embedding(x)
     want = plain.embedding(ids, we["weight"]) + plain.embedding([3, 4, 5, 6, 0, 1], wp["weight"])
     np.testing.assert_allclose(_np(x), want, atol=1e-7)
-    assert pos.max_positions == 20
-    assert get_part("position", "none")(_spec("none", {}, [])).max_positions is None
+    assert emb.info()["max_positions"] == 20
+    nopos = _harness("embedding", _spec("token_embedding", {"vocab_size": 77, "width": 48}, ["weight"]), torch.float32,
+                     position=_spec("none", {}, []), seed=1)
+    assert nopos.info()["max_positions"] is None
+    nopos.set_step([(3, 4), (0, 2)], ids)
+    nopos.run_embedding(x)
+    np.testing.assert_allclose(_np(x), plain.embedding(ids, nopos.tensors()["weight"]), atol=1e-7)
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("activation,layout", [("gelu_new", "in_out"), ("gelu", "out_in")])
 def test_dense_mlp_part(dtype, tol, activation, layout):
-    from sandyrt_b200.registry import get_part
-
-    part = get_part("feed_forward", "dense_mlp")(_spec(
+    part = _harness("feed_forward", _spec(
         "dense_mlp", {"width": 64, "inner": 200, "activation": activation, "weight_layout": layout},
-        ["up.weight", "up.bias", "down.weight", "down.bias"]))
-    w = _random_bind(part, 3, dtype)
-    ctx, _ = _ctx([], [(0, 9)], dtype)
+        ["up.weight", "up.bias", "down.weight", "down.bias"]), dtype, seed=3)
+    w = part.tensors()
+    part.set_step([(0, 9)])
     h = torch.randn(9, 64, device=DEV).to(dtype)
     x = torch.randn(9, 64, device=DEV)
     x0 = _np(x).copy()
-    part.forward(ctx, h, x)
+    part.run_feed_forward(h, x)
     store = "bf16" if dtype == torch.bfloat16 else "f32"
     rnd = plain.round_bf16 if store == "bf16" else (lambda a: a)
     wt = (lambda a: a) if layout == "in_out" else (lambda a: a.T)
@@ -119,6 +88,7 @@ def test_dense_mlp_part(dtype, tol, activation, layout):
     g = rnd(plain.gelu_new(u) if activation == "gelu_new" else plain.gelu_erf(u))
     want = x0 + plain.linear_in_out(g, rnd(wt(w["down.weight"])), rnd(w["down.bias"]))
     assert np.abs(_np(x) - want).max() < tol
+    assert part.info()["weight_bytes"] == (2 * 64 * 200 + 200 + 64) * (2 if dtype == torch.bfloat16 else 4)
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 2e-2)])
@@ -126,39 +96,23 @@ def test_dense_mlp_part(dtype, tol, activation, layout):
 def test_attention_part_whole_then_in_portions(dtype, tol, n_heads, n_kv_heads, head_dim, window):
     """The attention part over its own cache: a sequence in one step equals the same
     sequence in two portions plus single tokens (grouped heads and a window included)."""
-    from sandyrt_b200.parts.base import LayerCallCtx
-    from sandyrt_b200.registry import get_part
-
     width = 80
-    part = get_part("mixer", "causal_attention")(_spec(
-        "causal_attention", {"width": width, "n_heads": n_heads, "n_kv_heads": n_kv_heads, "head_dim": head_dim,
-                             "scale": 0.3, "window": window, "weight_layout": "out_in"},
-        ["qkv.weight", "qkv.bias", "out.weight", "out.bias"]))
-    w = _random_bind(part, 4, dtype)
+    spec = _spec("causal_attention", {"width": width, "n_heads": n_heads, "n_kv_heads": n_kv_heads, "head_dim": head_dim,
+                                      "scale": 0.3, "window": window, "weight_layout": "out_in"},
+                 ["qkv.weight", "qkv.bias", "out.weight", "out.bias"])
     T = 37
     h_all = (torch.randn(T, width, device=DEV) * 1.5).to(dtype)
+    w = None
 
     def run(cuts):
+        nonlocal w
+        part = _harness("mixer", spec, dtype, seed=4)      # a fresh cache; the same seed gives the same tensors
+        w = part.tensors()
         outs, before = [], 0
-        ctx, cm = None, None
         for n in cuts:
-            if ctx is None:
-                ctx, cm = _ctx([part.cache_spec()], [(0, n)], dtype)
-            else:
-                cm.alloc.commit(0, before)
-                cm.alloc.reserve(0, before + n)
-                bl = cm.alloc.block_list(0, 0)
-                table = torch.full((1, max(len(bl), 1)), -1, dtype=torch.int32)
-                table[0, :len(bl)] = torch.tensor(bl, dtype=torch.int32)
-                ctx.block_tables = {0: table.to(DEV)}
-                ctx.n_tokens = n
-                ctx.positions = torch.arange(before, before + n, dtype=torch.int32, device=DEV)
-                ctx.token_seq = torch.zeros(n, dtype=torch.int32, device=DEV)
-                ctx.q_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
-                ctx.kv_before = torch.tensor([before], dtype=torch.int32, device=DEV)
-                ctx.host_q_lens, ctx.host_kv_before, ctx.max_q_len, ctx.max_kv_len = [n], [before], n, before + n
+            part.set_step([(before, n)])
             x = torch.zeros(n, width, device=DEV)
-            part.forward(ctx, h_all[before:before + n].contiguous(), x, LayerCallCtx(0, True))
+            part.run_mixer(h_all[before:before + n].contiguous(), x)
             outs.append(_np(x))
             before += n
         return np.concatenate(outs)
