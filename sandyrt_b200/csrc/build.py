@@ -78,7 +78,21 @@ def _source_hash(name: str) -> str:
     return h.hexdigest()
 
 
+_build_dir_cache: Optional[str] = None
+_build_dir_lock = threading.Lock()
+
+
 def _build_dir() -> str:
+    """Where the libraries are built; decided once (the probe below must not race with itself when
+    several libraries are built at a time)."""
+    global _build_dir_cache
+    with _build_dir_lock:
+        if _build_dir_cache is None:
+            _build_dir_cache = _choose_build_dir()
+        return _build_dir_cache
+
+
+def _choose_build_dir() -> str:
     env = os.environ.get("SANDYRT_BUILD_DIR")
     if env:
         os.makedirs(env, exist_ok=True)
