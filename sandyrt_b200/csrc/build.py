@@ -65,7 +65,8 @@ def _find_nvcc() -> str:
 
 
 def _headers() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
+    """Headers the kernel sources include (sandy_kernels.h only declares their entry points for the host library)."""
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")) and f != "sandy_kernels.h")
 
 
 def _source_hash(name: str) -> str:

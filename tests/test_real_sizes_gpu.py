@@ -219,6 +219,34 @@ def test_many_requests_decoding_together_with_page_reuse(real_dirs, real_plain, 
     assert eng.cache.alloc.pools[0].free_pages == pool_pages
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_requests", [1, 8])
+def test_small_batches_decoding(real_dirs, real_plain, n_requests, dtype):
+    """Decode steps of 1 and of 8 requests (the shapes the fused attention-block kernel takes in
+    bfloat16: one block per token and head) over 40 single tokens each, after prompts of different
+    lengths, so that contexts cross page edges at different steps."""
+    from sandyrt_b200.engine.step import StepEntry
+
+    name = "small-2L"
+    eng = _engine(real_dirs[name], dtype, max_tokens=2048, max_requests=8)
+    oracle = real_plain(name, STORE[dtype])
+    lengths = [1, 15, 16, 17, 70, 129, 33, 250][:n_requests]
+    seqs = [_ids(name, n + 40, seed=300 + i) for i, n in enumerate(lengths)]
+    got = [[] for _ in seqs]
+    out = eng.step([StepEntry(i, s[:lengths[i]], [lengths[i] - 1]) for i, s in enumerate(seqs)]).cpu().numpy()
+    for i in range(n_requests):
+        got[i].append(out[i].copy())
+    for step in range(40):
+        out = eng.step([StepEntry(i, [s[lengths[i] + step]], [0]) for i, s in enumerate(seqs)]).cpu().numpy()
+        for i in range(n_requests):
+            got[i].append(out[i].copy())
+    eng.check_status()
+    for i, s in enumerate(seqs):
+        want = oracle.logits(s, rows=list(range(lengths[i] - 1, lengths[i] + 40)))
+        _close(np.stack(got[i]), want, dtype, f"request {i} of {n_requests} decoding")
+    eng.cache.alloc.check()
+
+
 def test_greedy_generation_with_bursts_at_real_sizes(real_dirs, real_plain):
     """(iv) the entry point with bursts of decode steps, float32: the same tokens as the plain
     implementation's greedy loop."""
