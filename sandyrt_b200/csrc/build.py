@@ -186,8 +186,7 @@ def load_library(name: str) -> ctypes.CDLL:
 # ---- the host library (sandyrt_b200/core/*.cpp -> libsandy_core.so) ---------------------------------
 CORE_DIR = os.path.join(os.path.dirname(CSRC_DIR), "core")
 CORE_NAME = "libsandy_core"
-CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-fvisibility-inlines-hidden", "-Wall",
-             "-Wno-unused-function"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function"]
 # -Bsymbolic: the library binds its own template instantiations (std::regex and the like) instead of
 # same-named ones another library of the process may export (torch does, built against another ABI).
 LINK_FLAGS = ["-Wl,-Bsymbolic"]
@@ -228,9 +227,11 @@ def compile_core(verbose: bool = True) -> str:
     the CUDA runtime.  No device code is in it; the kernels stay in their own libraries."""
     nvcc = _find_nvcc()
     cuda_home = os.path.dirname(os.path.dirname(os.path.realpath(nvcc)))
-    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    # the system's compiler first: it links the C++ runtime the rest of the process uses ($CXX may name a
+    # toolchain with a runtime of its own, linked statically)
+    cxx = os.environ.get("SANDYRT_CXX") or shutil.which("g++") or shutil.which("c++") or os.environ.get("CXX")
     if not cxx:
-        raise KernelBuildError("no C++ compiler found (looked at $CXX, g++, c++); the host library cannot be built")
+        raise KernelBuildError("no C++ compiler found (looked at $SANDYRT_CXX, g++, c++, $CXX); the host library cannot be built")
     so = core_library_path()
     objdir = os.path.join(_build_dir(), f"core_obj_{os.getpid()}")
     os.makedirs(objdir, exist_ok=True)
