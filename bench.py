@@ -237,23 +237,30 @@ def decode_run(llm, batch, prompt_len, steps, warmup, rng, vocab, want_e2e=True)
     return dev_ms, (e2e_ms, e2e_h2d, e2e_d2h), mean_ctx, launches
 
 
-def prefill_run(engine, vocab, rng, n_prompts=2, prompt_len=1024, reps=5):
-    """Median device time of one step over n_prompts x prompt_len prompt tokens."""
+def prefill_run(engine, vocab, rng, n_prompts=2, prompt_len=1024, reps=5, hold_us=1500):
+    """Median time of one step over n_prompts x prompt_len prompt tokens: (device_ms, with_host_ms).
+    device_ms: the device's share.  A kernel that only waits (engine.hold) keeps the stream busy while
+    the host prepares and queues the step, so the step's copy and kernels run back to back behind it and
+    the events bracket them alone.  with_host_ms: the same step timed from the moment the host starts on
+    it with an idle device, preparation and launch latency included."""
     from sandyrt_b200.engine.step import StepEntry
 
     prompts = [rng.integers(0, vocab, size=prompt_len).tolist() for _ in range(n_prompts)]
-    times = []
-    for it in range(3 + reps):
+    device, with_host = [], []
+    for it in range(3 + 2 * reps):
         entries = [StepEntry(f"p{it}-{i}", p, [len(p) - 1]) for i, p in enumerate(prompts)]
+        held = it % 2 == 1
+        if held:
+            engine.hold(hold_us)
         engine.mark(0)
         engine.step(entries)
         engine.mark(1)
         if it >= 3:
-            times.append(engine.elapsed_ms())
+            (device if held else with_host).append(engine.elapsed_ms())
         for e in entries:
             engine.release(e.rid)
     engine.check_status()
-    return sorted(times)[len(times) // 2]
+    return sorted(device)[len(device) // 2], sorted(with_host)[len(with_host) // 2]
 
 
 def prefill_flops(cfg, n_prompts, prompt_len):
@@ -401,7 +408,7 @@ def main() -> int:
     roofline = roofline_of(llm, model, args.batch, mean_ctx, dev_ms, peaks)
 
     # ---- prefill of 2,048 tokens: 2 prompts x 1,024 in one step ----------------------------------
-    pf_ms = prefill_run(engine, vocab, rng)
+    pf_ms, pf_host_ms = prefill_run(engine, vocab, rng)
     pf_frac = prefill_flops(cfg, 2, 1024) / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)
 
     points, fp32 = {}, {}
@@ -417,7 +424,7 @@ def main() -> int:
         for b in (1, 8):
             d_ms, _, ctx, _ = decode_run(llm32, b, args.prompt_len, min(args.steps, 32), 3, rng, vocab, want_e2e=False)
             fp32[f"decode_b{b}"] = {"value": b / (d_ms / 1e3), "ms_per_step": d_ms, "mean_context": round(ctx, 1)}
-        p32 = prefill_run(llm32.engine, vocab, rng, reps=2)
+        p32, _ = prefill_run(llm32.engine, vocab, rng, reps=2)
         fp32["prefill"] = {"value": 2048 / (p32 / 1e3), "tokens": 2048, "ms": p32}
 
     clock_info = clocks.stop()
@@ -435,7 +442,7 @@ def main() -> int:
                 "h2d_bytes_per_step": round(e2e_h2d, 1), "d2h_bytes_per_step": round(e2e_d2h, 1),
                 "steps_per_burst": 8, "bursts_queued_ahead": True},
         "gpu_launches": launches_per_step * args.steps, "launches_per_step": launches_per_step,
-        "prefill": {"value": 2048 / (pf_ms / 1e3), "tokens": 2048, "ms": pf_ms, "frac": pf_frac,
+        "prefill": {"value": 2048 / (pf_ms / 1e3), "tokens": 2048, "ms": pf_ms, "ms_with_host": pf_host_ms, "frac": pf_frac,
                     "peak": f"{peaks['bf16_tflops']} TFLOP/s bf16 of {peaks['source']}"},
         "roofline": roofline,
         "points": points,

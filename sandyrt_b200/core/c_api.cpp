@@ -969,6 +969,14 @@ SANDY_EXPORT int sandy_engine_mark(void* engine, int which) {
         },
         1);
 }
+SANDY_EXPORT int sandy_engine_hold(void* engine, int microseconds) {
+    return guarded(
+        [&]() {
+            ops::spin(((EngineBox*)engine)->engine->stream(), (long long)microseconds * 1000);
+            return 0;
+        },
+        1);
+}
 SANDY_EXPORT float sandy_engine_elapsed_ms(void* engine) {
     return guarded(
         [&]() {

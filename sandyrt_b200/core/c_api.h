@@ -124,6 +124,9 @@ int sandy_engine_synchronize(void* engine);
 void* sandy_engine_stream(void* engine);
 /* device time in milliseconds between two marks on the engine's stream */
 int sandy_engine_mark(void* engine, int which);
+/* Keeps the engine's stream busy for so many microseconds (a kernel that only waits), so that what the
+   host queues meanwhile runs back to back behind it: for timing the device's share of a step. */
+int sandy_engine_hold(void* engine, int microseconds);
 float sandy_engine_elapsed_ms(void* engine);
 
 #ifdef __cplusplus

@@ -236,30 +236,37 @@ void gemm_tc(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bi
         auto hit = g_tiles.find(key);
         if (hit != g_tiles.end()) tile_n = hit->second;
         else if (M >= kGemmTuneMinRows && !capturing(l.stream)) {
-            // timed without the cache write: the scratch runs must not touch pages
+            // timed without the cache write: the scratch runs must not touch pages.  A product that adds
+            // into its own output (x += ...) is timed adding into the scratch, the way it will run.
             DeviceBuffer scratch((size_t)M * (size_t)N * out.elem_size());
+            cuda_check(cudaMemsetAsync(scratch.get(), 0, (size_t)M * (size_t)N * out.elem_size(), l.stream), "clearing the tuner's scratch");
             Tensor dst = out;
             dst.data = scratch.get();
             dst.ld = N;
+            const bool in_place = residual && residual->data == out.data;
+            const Tensor* tune_res = in_place ? &dst : residual;
             cudaEvent_t e0, e1;
             cuda_check(cudaEventCreate(&e0), "creating an event");
             cuda_check(cudaEventCreate(&e1), "creating an event");
             float best_ms = 1e30f;
             int best = 0;
+            static const bool tune_log = std::getenv("SANDYRT_TUNE_LOG") != nullptr;      // what the tuner saw, on stderr
             for (int tile : kGemmVariants) {
-                launch_tc(l, g, tile, dst, residual, nullptr);
+                launch_tc(l, g, tile, dst, tune_res, nullptr);
                 // A launch costs the host about as long as one of these kernels takes the GPU, so timed
                 // naively the host's pace is what is measured; here the GPU is kept busy with a spin kernel
                 // while the launches queue up behind it.
                 spin(l.stream, 300000);
                 cudaEventRecord(e0, l.stream);
-                for (int i = 0; i < kTuneLaunches; i++) launch_tc(l, g, tile, dst, residual, nullptr);
+                for (int i = 0; i < kTuneLaunches; i++) launch_tc(l, g, tile, dst, tune_res, nullptr);
                 cudaEventRecord(e1, l.stream);
                 cuda_check(cudaEventSynchronize(e1), "timing a product");
                 float ms = 0;
                 cudaEventElapsedTime(&ms, e0, e1);
                 if (ms < best_ms) { best_ms = ms; best = tile; }
+                if (tune_log) fprintf(stderr, "[sandyrt_b200] product %lld x %lld x %lld, tile %d: %.2f us\n", (long long)M, (long long)N, (long long)K, tile, ms * 1e3f / kTuneLaunches);
             }
+            if (tune_log) fprintf(stderr, "[sandyrt_b200] product %lld x %lld x %lld: tile %d\n", (long long)M, (long long)N, (long long)K, best);
             cudaEventDestroy(e0);
             cudaEventDestroy(e1);
             g_tiles[key] = best;
@@ -273,18 +280,6 @@ void gemm_tc(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bi
 // ---- the weight-streaming product ---------------------------------------------------------------------
 constexpr int kSkinnyNormMaxRows = 16;
 constexpr int kSkinnyNormMaxK = 2048;
-// Between 17 and 64 rows neither kernel always wins (measured at 64 rows on GPT-2 small: the
-// up-projection, 3,072 columns, 5.9 us on tcgen05 against 10.7 us skinny; the out-projection, 768
-// columns, 6.1 against 4.2: a 128 x 64 tile per CTA leaves most SMs idle when there are few columns).
-// The two kernels add in different orders, so the choice is a fixed rule of the shape and never a
-// timing: the same batch gives the same bfloat16 tokens in every process.
-constexpr int kSmallTcMinRows = 33;
-constexpr int kSmallTcMinCols = 2048;
-
-bool small_gemm_prefers_tc(int64_t M, int64_t N, int64_t K) {
-    return M >= kSmallTcMinRows && N >= kSmallTcMinCols && tensor_core_gemm_supported(K, N);
-}
-
 bool skinny_norm_fusable(const FusedNorm& n, int64_t K, DType out_dtype) {
     return n.gamma.dtype == DType::BF16 && out_dtype == DType::BF16 && n.x.dtype == DType::F32 &&
            n.x.rows <= kSkinnyNormMaxRows && K <= kSkinnyNormMaxK && n.x.ld % 4 == 0 && !((uintptr_t)n.x.data & 15) &&
@@ -321,6 +316,54 @@ void gemm_skinny(const Launch& l, const Tensor* a, const FusedNorm* norm, const 
              kv ? kv->token_seq : nullptr, kv ? kv->positions : nullptr, kv ? kv->q_cols : 0, kv ? kv->kv_cols : 0,
              c ? c->head_dim : 0, c ? c->page_size : 0, c ? c->num_pages : 0, l.kernel_status, l.stream),
           "gemm_skinny(M=" + std::to_string(M) + ",N=" + std::to_string(N) + ",K=" + std::to_string(K) + ")");
+    if (kv) kv->written = true;
+}
+
+// ---- 17 to 64 rows on the tensor cores -----------------------------------------------------------------
+// Which kernel a product of 17 to 64 rows gets.  Timed one kernel after itself the tcgen05 kernel with
+// 64-wide tiles wins the up-projection (3072 x 768 at 64 rows: 6.8 us against 9.8 streaming) and split-K
+// the down-projection (768 x 3072: 8.2 against 11.2) and the vocabulary (50257 x 768: 26 against 98).
+// Inside a decode step of 64 requests, where a kernel's set-up and first loads run under the tail of the
+// kernel before it if its blocks find room beside that kernel's, the streaming kernel with its small blocks
+// beats the tiled one on the up-projection (step 0.723 ms against 0.756), split-K keeps its lead on the
+// down-projection (0.756 against 0.820) and is level on the vocabulary.  So: split-K for a long K or very
+// many columns, streaming otherwise.  The kernels add in different orders, so the choice is a fixed rule
+// of the shape and never a timing: the same batch gives the same bfloat16 tokens in every process.
+constexpr int kSmallMinRows = 17;
+constexpr int kSplitKMinK = 2048;
+constexpr int kSplitKMinCols = 16384;
+
+SmallGemm small_gemm_kernel(int64_t M, int64_t N, int64_t K) {
+    if (M < kSmallMinRows) return SmallGemm::Skinny;
+    if (K >= kSplitKMinK || N >= kSplitKMinCols) return SmallGemm::SplitK;
+    return SmallGemm::Skinny;
+}
+
+void gemm_small(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bias, Tensor& out, Act act,
+                const Tensor* residual, KVTarget* kv) {
+    const int64_t M = a.rows, K = a.cols, N = w.rows;
+    if (a.dtype != DType::BF16 || w.dtype != DType::BF16) throw UnsupportedShape("gemm_small takes bfloat16 operands");
+    if (M > kSkinnyMaxRows) throw UnsupportedShape("gemm_small takes at most 64 rows, got " + std::to_string(M));
+    if (w.cols != K || out.rows != M || out.cols != N)
+        throw KernelError("gemm_small: shapes disagree: a " + dims(a) + ", w " + dims(w) + ", out " + dims(out));
+    if (K % 8 || w.ld % 8 || a.ld % 8 || ((uintptr_t)w.data & 15) || ((uintptr_t)a.data & 15))
+        throw UnsupportedShape("gemm_small: K=" + std::to_string(K) + " and the row pitches must be multiples of 8 elements, operands 16-byte aligned");
+    if (residual && (residual->dtype != DType::F32 || residual->rows != M || residual->cols != N))
+        throw KernelError("gemm_small: residual must be float32 [M, N]");
+    if (bias && (bias->dtype != DType::BF16 || bias->numel() != N)) throw KernelError("gemm_small: bias must be bfloat16 [N]");
+    const KVView* c = kv ? &kv->cache : nullptr;
+    if (kv && (c->dtype != DType::BF16 || out.dtype != DType::BF16 || kv->kv_cols != c->n_kv_heads * c->head_dim ||
+               kv->q_cols + 2 * kv->kv_cols != N))
+        throw KernelError("gemm_small: the key/value target does not match the product");
+    static auto fn = SANDY_KERNEL(gemm_small, sandy_gemm_small);
+    OpTimer timer(l, kv ? "product, tcgen05 split-K (+ cache write)" : "product, tcgen05 split-K",
+                  tensor_bytes(&a) + tensor_bytes(&w) + tensor_bytes(&out) + 2 * tensor_bytes(residual), 2.0 * M * N * K);
+    check(fn(a.data, w.data, bias ? bias->data : nullptr, residual ? (const float*)residual->data : nullptr, out.data, (int)M,
+             (int)N, (int)K, (int)a.ld, (int)w.ld, residual ? (int)residual->ld : 0, (int)out.ld, (int)act, code_of(out.dtype),
+             c ? c->k : nullptr, c ? c->v : nullptr, c ? c->page_stride : 0, kv ? kv->block_table : nullptr, kv ? kv->max_blocks : 0,
+             kv ? kv->token_seq : nullptr, kv ? kv->positions : nullptr, kv ? kv->q_cols : 0, kv ? kv->kv_cols : 0,
+             c ? c->head_dim : 0, c ? c->page_size : 0, c ? c->num_pages : 0, l.kernel_status, l.stream),
+          "gemm_small(M=" + std::to_string(M) + ",N=" + std::to_string(N) + ",K=" + std::to_string(K) + ")");
     if (kv) kv->written = true;
 }
 

@@ -82,7 +82,12 @@ bool skinny_norm_fusable(const FusedNorm& n, int64_t K, DType out_dtype);
 void gemm_skinny(const Launch& l, const Tensor* a, const FusedNorm* norm, const Tensor& w, const Tensor* bias, Tensor& out,
                  Act act, const Tensor* residual, KVTarget* kv = nullptr);
 constexpr int kSkinnyMaxRows = 64;
-bool small_gemm_prefers_tc(int64_t M, int64_t N, int64_t K);
+// tcgen05 with the weight as the wide operand and K split over a cluster, for 17 to 64 rows (gemm_small.cu).
+// small_gemm_kernel: which kernel a bfloat16 product of 17 to 64 rows gets, from its shape alone.
+enum class SmallGemm { Skinny, SplitK };
+SmallGemm small_gemm_kernel(int64_t M, int64_t N, int64_t K);
+void gemm_small(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bias, Tensor& out, Act act,
+                const Tensor* residual, KVTarget* kv = nullptr);
 
 void kv_append(const Launch& l, const Tensor& k_src, const Tensor& v_src, const KVView& cache, const int* block_table,
                int max_blocks, const int* token_seq, const int* positions);

@@ -92,8 +92,8 @@ void Linear::run(StepContext& ctx, NormedInput* lazy, const Tensor* a, Tensor& o
         ops::FusedNorm fused;
         const bool fuse = lazy && lazy->fusable(fused) && ops::skinny_norm_fusable(fused, in_, DType::BF16);
         if (!fuse && lazy) a = &lazy->tensor();
-        if (!fuse && !kv && ops::small_gemm_prefers_tc(rows, out_, in_)) {
-            ops::gemm_tc(l, *a, weight_.view, bias, out, act, residual, 64);
+        if (!fuse && ops::small_gemm_kernel(rows, out_, in_) == ops::SmallGemm::SplitK) {
+            ops::gemm_small(l, *a, weight_.view, bias, out, act, residual, kv);
             return;
         }
         ops::gemm_skinny(l, fuse ? nullptr : a, fuse ? &fused : nullptr, weight_.view, bias, out, act, residual, kv);

@@ -39,6 +39,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_tc": [],
     "gemm_tc2": [],
     "gemm_skinny": [],
+    "gemm_small": [],
     "attention": [],
     "attention_decode": [],
     "attention_decode_bulk": [],

@@ -16,7 +16,10 @@
 //   warp 1      allocates BN columns of tensor memory; one elected lane issues four
 //               tcgen05.mma (128 x BN x 16) per stage and commits each stage back to the ring
 //   warps 2..5  when the last commit lands, read the accumulator with tcgen05.ld (each warp its
-//               32 lanes = 32 rows), apply the epilogue and store
+//               32 lanes = 32 rows), apply the epilogue and write back: above one tile of rows
+//               through tiles in shared memory (the ring, idle by then) that TMA stores, or
+//               reduce-adds where the residual is the output itself; else from the registers
+//               (write_back_warp in tcgen05.cuh)
 // Rows and columns past M, N, K are zero-filled by TMA on the way in and masked on the way
 // out, so any M and N are taken; K must be a multiple of 8 (TMA wants 16-byte row pitches).
 // For a given output element the k-steps are always added in ascending order, so a row's
@@ -36,12 +39,13 @@ struct SmemLayout {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(STAGES * STAGE_BYTES >= 8 * EPI_WARP_BYTES, "the one-tile kernel stages its write-back in the ring");
 };
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(NUM_THREADS)
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               EpilogueArgs ep, int M, int N, int K, int* __restrict__ status) {
+               const __grid_constant__ CUtensorMap map_out, EpilogueArgs ep, int M, int N, int K, int* __restrict__ status) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -126,6 +130,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // ---------------- epilogue: warps 2..5 ----------------
         const int quarter = warp & 3;         // the TMEM lanes this warp may read: 32*quarter ..
+        float bias[BN / 32];
+        load_bias(bias, ep, n0, N);
         pdl_wait();              // out and residual may still be in use by the kernel before
         const bool ready = mbar_wait(accum_bar, 0);
         if (!ready && lane == 0 && status) atomicOr(status, 4);
@@ -134,15 +140,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int kv_page, kv_slot;
         kv_row_target(ep.kv, row, M, kv_page, kv_slot);
         if (ready) {
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                float4 res[8];
-                const bool have_res = load_residual(res, row, n0 + c * 32, ep, M, N);
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
-                tmem_wait_ld();
-                store_chunk(r, row, n0 + c * 32, ep, M, N, res, have_res, kv_page, kv_slot, status);
-            }
+            // every MMA has completed, so nothing reads the ring any more: the warps stage their tiles in it
+            write_back_warp<BN / 32, 2>(tmem_base + ((uint32_t)(quarter * 32) << 16), stage_base + quarter * 2 * EPI_WARP_BYTES,
+                                     m0 + quarter * 32, n0, ep, &map_out, M, N, kv_page, kv_slot, status, bias, [] {});
         }
     }
     tc_fence_before();
@@ -167,16 +167,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // Tiles are numbered m-fastest, so CTAs that run side by side share a W tile in L2.
 constexpr int P_THREADS = 320;
 constexpr int P_EPI_WARPS = 8;
+// Shared memory of the persistent form: its ring never rests, so the write-back warps get staging tiles
+// of their own between the ring and the barriers.
+template <int BN, int STAGES>
+constexpr int persistent_smem() { return SmemLayout<BN, STAGES>::TOTAL + P_EPI_WARPS * EPI_WARP_BYTES; }
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                          EpilogueArgs ep, int M, int N, int K, int* __restrict__ status) {
+                          const __grid_constant__ CUtensorMap map_out, EpilogueArgs ep, int M, int N, int K,
+                          int* __restrict__ status) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+    uint8_t* epi_tiles = smem + STAGES * L::STAGE_BYTES;          // 1024-byte aligned, a tile per write-back warp
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_tiles + P_EPI_WARPS * EPI_WARP_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* acc_full = empty_bar + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;            // [2]
@@ -272,8 +278,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     } else {
         // ---------------- epilogue: warps 2..9 ----------------
         const int quarter = warp & 3;                  // the TMEM lanes this warp may read
+        // The tile's columns are halved between the two warps of a quarter.  (Half of a 64-column tile is a
+        // single chunk: narrower than a bfloat16 staging tile, so it is written back from the registers, which
+        // for the few rows this width is chosen for is the quicker way anyhow.)
         const int half = (warp - 2) >> 2;              // which half of the tile's columns
         constexpr int CHUNKS = BN / 32 / 2;            // 32-column chunks per warp
+        uint8_t* tile_mem = epi_tiles + (warp - 2) * EPI_WARP_BYTES;
         bool dead = false;
         int ti = 0;
         pdl_wait();                 // out and residual may still be in use by the kernel before
@@ -283,6 +293,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             const int row = m0 + quarter * 32 + lane;
             int kv_page, kv_slot;
             kv_row_target(ep.kv, row, M, kv_page, kv_slot);
+            float bias[CHUNKS];
+            load_bias(bias, ep, n0 + half * CHUNKS * 32, N);
             // A warp whose wait ran out keeps walking the tiles but touches nothing any more.
             if (!dead && !mbar_wait(&acc_full[b], (ti >> 1) & 1)) {
                 if (lane == 0 && status) atomicOr(status, 4);
@@ -290,22 +302,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             }
             if (dead) continue;
             tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < CHUNKS; c++) {
-                const int cc = half * CHUNKS + c;
-                float4 res[8];
-                const bool have_res = load_residual(res, row, n0 + cc * 32, ep, M, N);
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + cc * 32), r);
-                tmem_wait_ld();
-                if (c == CHUNKS - 1) {
-                    // everything this warp needs of the accumulator is in registers: hand it back
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[b]);
-                }
-                store_chunk(r, row, n0 + cc * 32, ep, M, N, res, have_res, kv_page, kv_slot, status);
-            }
+            write_back_warp<CHUNKS, 1>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * CHUNKS * 32), tile_mem,
+                                    m0 + quarter * 32, n0 + half * CHUNKS * 32, ep, &map_out, M, N, kv_page, kv_slot, status, bias, [&] {
+                                        // everything this warp needs of the accumulator is in registers: hand it back
+                                        tc_fence_before();
+                                        __syncwarp();
+                                        if (lane == 0) mbar_arrive(&acc_empty[b]);
+                                    });
         }
     }
     tc_fence_before();
@@ -318,8 +321,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 }
 
 template <int BN, int STAGES>
-int launch(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs& ep, int M, int N, int K, int* status,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const EpilogueArgs& ep, int M, int N, int K,
+           int* status, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
     static bool configured = false;
     if (!configured) {
@@ -329,7 +332,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs& ep,
         configured = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    return sandy_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(NUM_THREADS), L::TOTAL, stream, ma, mw, ep, M, N, K, status);
+    return sandy_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(NUM_THREADS), L::TOTAL, stream, ma, mw, mo, ep, M, N, K, status);
 }
 
 // Which kernel and tile width for a product.  Both kernels are bound by how fast an SM can pull
@@ -368,13 +371,13 @@ int choose_tile(int M, int N, int K) {
 }
 
 template <int BN, int STAGES>
-int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs& ep, int M, int N, int K,
-                      int* status, cudaStream_t stream) {
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const EpilogueArgs& ep, int M,
+                      int N, int K, int* status, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
     static int sms = 0;
     if (sms == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, persistent_smem<BN, STAGES>());
         if (e != cudaSuccess) return (int)e;
         int dev = 0, n = 0;
         e = cudaGetDevice(&dev);
@@ -384,7 +387,7 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const Epilog
     }
     const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = (int)(tiles < sms ? tiles : sms);
-    return sandy_launch(gemm_tc_persistent_kernel<BN, STAGES>, dim3(grid), dim3(P_THREADS), L::TOTAL, stream, ma, mw, ep, M,
+    return sandy_launch(gemm_tc_persistent_kernel<BN, STAGES>, dim3(grid), dim3(P_THREADS), persistent_smem<BN, STAGES>(), stream, ma, mw, mo, ep, M,
                         N, K, status);
 }
 
@@ -420,14 +423,16 @@ SANDY_API int sandy_gemm_tc(const void* a, const void* w, const void* bias, cons
             page_stride % 8 != 0)
             return SANDY_ERR_ARGUMENT;
     }
-    EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0, kv};
+    EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0, kv, 0};
+    CUtensorMap mo;
+    get_out_map(ep, M, N, &mo);
     switch (tile_n) {
-        case -64: return launch<64, 4>(ma, mw, ep, M, N, K, status, stream);
-        case -128: return launch<128, 3>(ma, mw, ep, M, N, K, status, stream);
-        case -256: return launch<256, 4>(ma, mw, ep, M, N, K, status, stream);
-        case 64: return launch_persistent<64, 8>(ma, mw, ep, M, N, K, status, stream);
-        case 128: return launch_persistent<128, 6>(ma, mw, ep, M, N, K, status, stream);
-        case 256: return launch_persistent<256, 4>(ma, mw, ep, M, N, K, status, stream);
+        case -64: return launch<64, 4>(ma, mw, mo, ep, M, N, K, status, stream);
+        case -128: return launch<128, 3>(ma, mw, mo, ep, M, N, K, status, stream);
+        case -256: return launch<256, 4>(ma, mw, mo, ep, M, N, K, status, stream);
+        case 64: return launch_persistent<64, 7>(ma, mw, mo, ep, M, N, K, status, stream);
+        case 128: return launch_persistent<128, 6>(ma, mw, mo, ep, M, N, K, status, stream);
+        case 256: return launch_persistent<256, 4>(ma, mw, mo, ep, M, N, K, status, stream);
         default: return SANDY_ERR_UNSUPPORTED;
     }
 }

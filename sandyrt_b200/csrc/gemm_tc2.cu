@@ -86,18 +86,20 @@ struct PairLayout {
     static constexpr int A_BYTES = BM * BK * 2;             // this CTA's 128 rows of A
     static constexpr int B_BYTES = (BN / 2) * BK * 2;       // this CTA's half of the W rows
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    // the ring, a staging tile for each write-back warp, the barriers
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 8 * EPI_WARP_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                EpilogueArgs ep, int M, int N, int K, int* __restrict__ status) {
+                const __grid_constant__ CUtensorMap map_out, EpilogueArgs ep, int M, int N, int K, int* __restrict__ status) {
     using L = PairLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+    uint8_t* epi_tiles = smem + STAGES * L::STAGE_BYTES;          // 1024-byte aligned, a tile per write-back warp
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_tiles + 8 * EPI_WARP_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* acc_full = empty_bar + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;            // [2]
@@ -198,6 +200,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;
         constexpr int CHUNKS = BN / 32 / 2;
+        uint8_t* tile_mem = epi_tiles + (warp - 2) * EPI_WARP_BYTES;
         bool dead = false;
         int ti = 0;
         pdl_wait();              // out and residual may still be in use by the kernel before
@@ -207,6 +210,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int row = m0 + quarter * 32 + lane;
             int kv_page, kv_slot;
             kv_row_target(ep.kv, row, M, kv_page, kv_slot);
+            float bias[CHUNKS];
+            load_bias(bias, ep, n0 + half * CHUNKS * 32, N);
             // A warp whose wait ran out keeps walking the tiles but touches nothing any more.
             if (!dead && !mbar_wait(&acc_full[b], (ti >> 1) & 1)) {
                 if (lane == 0 && status) atomicOr(status, 4);
@@ -214,22 +219,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
             if (dead) continue;
             tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < CHUNKS; c++) {
-                const int cc = half * CHUNKS + c;
-                float4 res[8];
-                const bool have_res = load_residual(res, row, n0 + cc * 32, ep, M, N);
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + cc * 32), r);
-                tmem_wait_ld();
-                if (c == CHUNKS - 1) {
-                    // everything this warp needs of the accumulator is in registers: hand it back
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(in_cta(smem_u32(&acc_empty[b]), 0));
-                }
-                store_chunk(r, row, n0 + cc * 32, ep, M, N, res, have_res, kv_page, kv_slot, status);
-            }
+            write_back_warp<CHUNKS, 1>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * CHUNKS * 32), tile_mem,
+                                    m0 + quarter * 32, n0 + half * CHUNKS * 32, ep, &map_out, M, N, kv_page, kv_slot, status, bias, [&] {
+                                        // everything this warp needs of the accumulator is in registers: hand it back
+                                        tc_fence_before();
+                                        __syncwarp();
+                                        if (lane == 0) mbar_arrive_cluster(in_cta(smem_u32(&acc_empty[b]), 0));
+                                    });
         }
     }
     tc_fence_before();
@@ -243,7 +239,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 template <int BN, int STAGES>
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs& ep, int M, int N, int K, int* status,
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const EpilogueArgs& ep, int M, int N, int K, int* status,
                 cudaStream_t stream) {
     using L = PairLayout<BN, STAGES>;
     auto kern = gemm_tc2_kernel<BN, STAGES>;
@@ -273,7 +269,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const EpilogueArgs
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = sandy_pdl_enabled() ? 2 : 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mw, ep, M, N, K, status);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mw, mo, ep, M, N, K, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -305,7 +301,9 @@ SANDY_API int sandy_gemm_tc2(const void* a, const void* w, const void* bias, con
             page_stride % 8 != 0)
             return SANDY_ERR_ARGUMENT;
     }
-    EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0, kv};
-    if (tile_n == 128) return launch_pair<128, 8>(ma, mw, ep, M, N, K, status, stream);
-    return launch_pair<256, 6>(ma, mw, ep, M, N, K, status, stream);
+    EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0, kv, 0};
+    CUtensorMap mo;
+    get_out_map(ep, M, N, &mo);
+    if (tile_n == 128) return launch_pair<128, 8>(ma, mw, mo, ep, M, N, K, status, stream);
+    return launch_pair<256, 6>(ma, mw, mo, ep, M, N, K, status, stream);
 }

@@ -1,7 +1,7 @@
 """Kernel micro-benchmarks: one kernel alone, inside a CUDA graph, on inputs larger than L2.
 
     python -m sandyrt_b200.csrc.microbench decode-attention [--heads 12] [--head-dim 64] [--page-size 16]
-    python -m sandyrt_b200.csrc.microbench gemm [--rows 2048] [--width 768] [--inner 3072] [--k-sweep]
+    python -m sandyrt_b200.csrc.microbench gemm [--rows 2048] [--width 768] [--inner 3072] [--layers 48] [--k-sweep]
     python -m sandyrt_b200.csrc.microbench prefill-attention [--heads 12] [--page-size 16] [--shape 2x1024+0 ...]
 
 decode-attention: the register kernel and the bulk-copy kernel of single-token attention on
@@ -78,19 +78,23 @@ def decode_attention(a) -> int:
 
 def gemm(a) -> int:
     """The tcgen05 product at the shapes of a prompt step, every tile choice; activations and
-    weights of `layers` distinct layers so that the operands do not sit in L2 between launches."""
+    weights of --layers distinct layers (48 by default: 170 to 230 MB of weights per shape, more
+    than L2 holds, so the weights come from memory as they do in a model)."""
     dev = torch.device("cuda:0")
     M = a.rows
     shapes = [("q/k/v", 3 * a.width, a.width, None, False), ("out-projection", a.width, a.width, None, True),
               ("up-projection", a.inner, a.width, "gelu_new", False), ("down-projection", a.width, a.inner, None, True)]
     print(f"rows {M}; us per launch (TFLOP/s) by tile width; negative: one tile per CTA; 2000+: two CTAs a tile")
-    layers = 12
+    layers = a.layers
     for name, N, K, act, res in shapes:
-        xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(layers)]
+        # inputs are a kernel's output in a model and sit in L2; four of them take turns here
+        x4 = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+        xs = [x4[l % 4] for l in range(layers)]
         ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05 for _ in range(layers)]
         bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
-        out = torch.empty(M, N, device=dev, dtype=torch.float32 if res else torch.bfloat16)
-        resid = torch.randn(M, N, device=dev, dtype=torch.float32) if res else None
+        # the residual products add into the float32 stream in place, as the blocks do
+        out = torch.zeros(M, N, device=dev, dtype=torch.float32 if res else torch.bfloat16)
+        resid = out if res else None
         line = f"{name:16s} {M}x{N}x{K}:"
         for tile in ops.GEMM_VARIANTS:
             def go(l, tile=tile):
@@ -101,6 +105,17 @@ def gemm(a) -> int:
             def go_skinny(l):
                 ops.gemm_skinny(xs[l], ws[l], bias, out, act=act, residual=resid)
             line += f"  skinny: {_time_graph(go_skinny, layers):6.1f}"
+
+            def go_small(l):
+                ops.gemm_small(xs[l], ws[l], bias, out, act=act, residual=resid)
+            line += f"  small ({ops.gemm_small_splits(N, K)} splits): {_time_graph(go_small, layers):6.1f}"
+        # the library's product with its bias alone (no activation, no residual, bfloat16 out): the yardstick
+        lib_out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+
+        def go_lib(l):
+            torch.addmm(bias, xs[l], ws[l].t(), out=lib_out)
+        us = _time_graph(go_lib, layers)
+        line += f"  cuBLAS: {us:6.1f} ({2.0 * M * N * K / us / 1e6:5.0f})"
         print(line, flush=True)
         ops.check_kernel_status(dev)
     if a.k_sweep:
@@ -109,7 +124,8 @@ def gemm(a) -> int:
         N = 3 * a.width
         print(f"K sweep at {M}x{N}, no bias, bfloat16 out: us (TFLOP/s)")
         for K in (64, 256, 768, 1536, 3072):
-            xs = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(layers)]
+            x4 = [torch.randn(M, K, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+            xs = [x4[l % 4] for l in range(layers)]
             ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05 for _ in range(layers)]
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
             line = f"K {K:5d}:"
@@ -176,6 +192,7 @@ def main(argv=None) -> int:
     g.add_argument("--width", type=int, default=768)
     g.add_argument("--inner", type=int, default=3072)
     g.add_argument("--k-sweep", action="store_true", help="also time the q/k/v output size at several K")
+    g.add_argument("--layers", type=int, default=48, help="distinct weights and inputs per shape")
     g.set_defaults(fn=gemm)
     pa = sub.add_parser("prefill-attention")
     pa.add_argument("--heads", type=int, default=12)

@@ -519,3 +519,54 @@ def gemm_skinny(a, w, bias, out, *, act=None, residual=None, norm=None, kv=None)
         ctypes.c_int(head_dim), ctypes.c_int(page_size), ctypes.c_int(num_pages), _p(kernel_status(w.device)),
         _stream())
     _check(code, f"gemm_skinny(M={M},N={N},K={K},norm={norm is not None},kv={kv is not None})")
+
+
+def gemm_small(a, w, bias, out, *, act=None, residual=None, kv=None) -> None:
+    """out = act(a @ w.T + bias) + residual for up to 64 rows on the tcgen05 tensor cores with the
+    weight as the instruction's wide operand and K split over a cluster's blocks (gemm_small.cu).
+    Same operand rules as gemm_tc; `kv` as in gemm_skinny."""
+    M, K = a.shape
+    N = w.shape[0]
+    _cuda(a, w, bias, out, residual)
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise UnsupportedShape("gemm_small takes bfloat16 operands")
+    if M > 64:
+        raise UnsupportedShape(f"gemm_small takes at most 64 rows, got {M}")
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_small: shapes disagree: a {(M, K)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_small: innermost stride must be 1")
+    if K % 8 or w.stride(0) % 8 or w.data_ptr() % 16 or a.stride(0) % 8 or a.data_ptr() % 16:
+        raise UnsupportedShape(f"gemm_small: K={K} and the row pitches must be multiples of 8 elements, "
+                               "operands 16-byte aligned")
+    if residual is not None and (residual.dtype != torch.float32 or residual.stride(1) != 1
+                                 or tuple(residual.shape) != (M, N)):
+        raise KernelError("gemm_small: residual must be float32 [M, N]")
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N):
+        raise KernelError("gemm_small: bias must be bfloat16 [N]")
+    kc = vc = table = tseq = tpos = None
+    page_stride = max_blocks = q_cols = kv_cols = head_dim = page_size = num_pages = 0
+    if kv is not None:
+        hkv, page_size, head_dim, page_stride, num_pages = _cache_args(kv.k_cache, kv.v_cache)
+        kc, vc, table, tseq, tpos = kv.k_cache, kv.v_cache, kv.block_table, kv.token_seq, kv.positions
+        _cuda(kc, vc, table, tseq, tpos)
+        _i32(table, "block_table"); _i32(tseq, "token_seq"); _i32(tpos, "positions")
+        q_cols, kv_cols, max_blocks = kv.q_cols, kv.kv_cols, table.shape[1]
+        if kc.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kv_cols != hkv * head_dim \
+                or q_cols + 2 * kv_cols != N or kv.head_dim != head_dim:
+            raise KernelError("gemm_small: the key/value target does not match the product")
+    lib = load_library("gemm_small")
+    code = lib.sandy_gemm_small(
+        _p(a), _p(w), _p(bias), _p(residual), _p(out), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_int(a.stride(0)), ctypes.c_int(w.stride(0)),
+        ctypes.c_int(0 if residual is None else residual.stride(0)), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(ACT_CODES[act]), ctypes.c_int(_dt(out)), _p(kc), _p(vc), ctypes.c_longlong(page_stride),
+        _p(table), ctypes.c_int(max_blocks), _p(tseq), _p(tpos), ctypes.c_int(q_cols), ctypes.c_int(kv_cols),
+        ctypes.c_int(head_dim), ctypes.c_int(page_size), ctypes.c_int(num_pages), _p(kernel_status(w.device)),
+        _stream())
+    _check(code, f"gemm_small(M={M},N={N},K={K},kv={kv is not None})")
+
+
+def gemm_small_splits(N: int, K: int) -> int:
+    """How many blocks share an output tile of gemm_small for this shape on this device."""
+    return int(load_library("gemm_small").sandy_gemm_small_splits(ctypes.c_int(N), ctypes.c_int(K)))

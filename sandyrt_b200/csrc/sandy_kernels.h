@@ -46,6 +46,14 @@ int sandy_gemm_skinny(const void* a, const float* x, int ldx, const void* gamma,
                       const int* block_table, int max_blocks, const int* token_seq, const int* positions, int q_cols,
                       int kv_cols, int head_dim, int page_size, int num_pages, int* status, cudaStream_t stream);
 
+/* gemm_small.cu */
+int sandy_gemm_small_splits(int N, int K);
+int sandy_gemm_small(const void* a, const void* w, const void* bias, const float* residual, void* out, int M, int N, int K,
+                     int lda, int ldw, int ldr, int ldc, int act, int out_dtype, void* k_cache, void* v_cache,
+                     long long page_stride, const int* block_table, int max_blocks, const int* token_seq,
+                     const int* positions, int q_cols, int kv_cols, int head_dim, int page_size, int num_pages, int* status,
+                     cudaStream_t stream);
+
 /* attention.cu */
 int sandy_kv_append(const void* k_src, const void* v_src, int ld_src, void* k_cache, void* v_cache, long long page_stride,
                     const int* block_table, int max_blocks, const int* token_seq, const int* positions, int n_tokens,

@@ -5,6 +5,7 @@
 
 #include <cuda.h>
 
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -148,6 +149,7 @@ struct EpilogueArgs {
     int act;
     int out_f32;             // 1: float out, 0: bfloat16 out
     KVWrite kv;
+    int tma_out;             // 1: the kernel's output tensor map is valid and the write-back goes through it
 };
 
 // The page (or -1) and the slot inside it where row `row`'s key and value belong.
@@ -176,14 +178,10 @@ __device__ __forceinline__ bool load_residual(float4 (&res)[8], int row, int col
 
 // Write-back of 32 consecutive columns of one row: bias, activation, residual, rounding, store.
 // kv_page, kv_slot: from kv_row_target, used when the chunk holds key or value columns.
+// my_bias: the bias of column col0 + lane (load_bias), handed round by shuffles.
 __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, int col0, const EpilogueArgs& ep, int M,
                                             int N, const float4 (&res)[8], bool have_res, int kv_page, int kv_slot,
-                                            int* status) {
-    // the chunk's 32 bias values: one load per lane, handed round by shuffles (32 scalar loads per
-    // thread were a trip to memory in front of every chunk's arithmetic)
-    const int lane = threadIdx.x & 31;
-    float my_bias = 0.0f;
-    if (ep.bias && col0 + lane < N) my_bias = __bfloat162float(ep.bias[col0 + lane]);
+                                            int* status, float my_bias) {
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; j++) v[j] = apply_act_fast(__uint_as_float(r[j]) + __shfl_sync(0xffffffffu, my_bias, j), ep.act);
@@ -275,6 +273,196 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, in
 }
 
 
+// ---- write-back through TMA stores -----------------------------------------------------------------
+// tcgen05.ld hands a thread 32 consecutive columns of ONE row (its tensor-memory lane).  Stored
+// straight from those registers (store_chunk above) a warp writes 32 pieces of 16 bytes in 32
+// different rows per instruction and the kernel sits in its write-back for longer than in its main
+// loop (measured on a 2048 x 2304 x 768 product: 13.6 us with register stores, 10.7 through the copy
+// engine; turning the chunk round in shared memory and storing whole row pieces was no faster than
+// the register stores).  So each warp builds its 32 rows x 128 bytes (64 bfloat16 or 32 float
+// columns) in a shared-memory tile in the 128-byte swizzle and one lane hands the tile to TMA:
+//   - rows past M and columns past N are clipped by the tensor map, so every M and N is taken;
+//   - a residual that is the output itself (x += ...) becomes a TMA reduce-add into x: the SM never
+//     reads the old value, and every element still receives exactly one addition;
+//   - key and value columns go into their cache pages from the registers, as in store_chunk.
+// A tensor map wants a 16-byte aligned base and row pitch, and the store clips rows in pieces of 16
+// bytes; products whose output does not fit that, or whose residual is another tensor than the output,
+// are written back by store_chunk.
+constexpr int EPI_WARP_BYTES = 32 * 128;                   // a warp's staging tile; 1024-byte aligned
+
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// This lane's 32 accumulator values of the chunk at global column col0 (its row: `row`): bias,
+// activation, rounding, into the warp's tile; `h` is the chunk's place in the tile (bfloat16: 0 or 1,
+// float: 0).  Key and value columns also go to the cache.
+// my_bias: the bias of column col0 + lane (load_bias).
+__device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], uint8_t* tile, int h, int row, int col0,
+                                            const EpilogueArgs& ep, int M, int N, int kv_page, int kv_slot, int* status,
+                                            float my_bias) {
+    const int lane = threadIdx.x & 31;
+    uint8_t* my_row = tile + lane * 128;
+    const int twist = lane & 7;                 // the 128-byte swizzle: 16-byte piece j of row l lies at piece j ^ (l % 8)
+    if (ep.out_f32) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                v[e] = apply_act_fast(__uint_as_float(r[4 * j + e]) + __shfl_sync(0xffffffffu, my_bias, 4 * j + e), ep.act);
+            *reinterpret_cast<float4*>(my_row + ((j ^ twist) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    } else {
+        const bool to_cache = ep.kv.k_cache && row < M && col0 + 32 > ep.kv.q_cols;
+        const bool page_ok = kv_page >= 0 && kv_page < ep.kv.num_pages;
+        if (to_cache && !page_ok && status) atomicOr(status, 8);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++)
+                v[e] = apply_act_fast(__uint_as_float(r[8 * q + e]) + __shfl_sync(0xffffffffu, my_bias, 8 * q + e), ep.act);
+            const __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+            uint4 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&h0);
+            pk.y = *reinterpret_cast<const uint32_t*>(&h1);
+            pk.z = *reinterpret_cast<const uint32_t*>(&h2);
+            pk.w = *reinterpret_cast<const uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(my_row + (((4 * h + q) ^ twist) << 4)) = pk;
+            // eight columns from a multiple of eight never straddle the query / key / value ranges or two
+            // heads (the host checks q_cols % 8 == 0 and head_dim % 16 == 0)
+            const int col = col0 + 8 * q;
+            if (to_cache && page_ok && col >= ep.kv.q_cols && col + 8 <= N) {
+                const int c = col - ep.kv.q_cols;
+                const bool is_v = c >= ep.kv.kv_cols;
+                const int c2 = is_v ? c - ep.kv.kv_cols : c;
+                const int head = c2 / ep.kv.head_dim, d = c2 % ep.kv.head_dim;
+                bf16* dst = (is_v ? ep.kv.v_cache : ep.kv.k_cache) + (size_t)kv_page * ep.kv.page_stride +
+                            ((size_t)head * ep.kv.page_size + kv_slot) * ep.kv.head_dim + d;
+                *reinterpret_cast<uint4*>(dst) = pk;
+            }
+        }
+    }
+}
+
+// One lane hands the warp's tile to TMA: output columns from col0, rows from row0.
+__device__ __forceinline__ void store_tile(const CUtensorMap* map_out, const uint8_t* tile, int col0, int row0, bool add) {
+    if (add)
+        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_out),
+                     "r"(smem_u32(tile)), "r"(col0), "r"(row0)
+                     : "memory");
+    else
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_out),
+                     "r"(smem_u32(tile)), "r"(col0), "r"(row0)
+                     : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// The bias values a lane needs in write_back_warp: of column col_first + 32 c + lane for each chunk c.
+// A trip to memory each, so the kernels ask for them before they wait for the accumulator (the bias is a
+// weight: no kernel writes it).
+template <int NCHUNKS>
+__device__ __forceinline__ void load_bias(float (&b)[NCHUNKS], const EpilogueArgs& ep, int col_first, int N) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int c = 0; c < NCHUNKS; c++) {
+        const int col = col_first + c * 32 + lane;
+        b[c] = (ep.bias && col < N) ? __bfloat162float(ep.bias[col]) : 0.0f;
+    }
+}
+
+template <int NCHUNKS>
+__device__ __forceinline__ float bias_of(const float (&b)[NCHUNKS], int c) {
+    float v = b[0];
+#pragma unroll
+    for (int k = 1; k < NCHUNKS; k++)
+        if (c == k) v = b[k];           // selects, so that b stays in registers under a rolled loop
+    return v;
+}
+
+// A warp's whole write-back: NCHUNKS chunks of 32 columns from tensor-memory address taddr (its lane
+// quarter, the first chunk's column); output rows row0 .. row0 + 31 (this lane: row0 + lane), first
+// column col_first.  tiles: the warp's NTILES staging tiles of EPI_WARP_BYTES each; with two, a tile is
+// filled while the copy engine still reads the other.  Chunks leave tensor memory two at a time (one
+// wait for both loads).  after_loads() runs once the last chunk has left tensor memory (the persistent
+// kernels hand the accumulator back there).
+template <int NCHUNKS, int NTILES, typename AfterLoads>
+__device__ __forceinline__ void write_back_warp(uint32_t taddr, uint8_t* tiles, int row0, int col_first, const EpilogueArgs& ep,
+                                                const CUtensorMap* map_out, int M, int N, int kv_page, int kv_slot, int* status,
+                                                const float (&bias)[NCHUNKS], AfterLoads after_loads) {
+    static_assert(NTILES == 1 || NTILES == 2, "one or two staging tiles");
+    const int lane = threadIdx.x & 31;
+    const int row = row0 + lane;
+    if (!ep.tma_out) {
+#pragma unroll 1
+        for (int c = 0; c < NCHUNKS; c++) {
+            float4 res[8];
+            const bool have_res = load_residual(res, row, col_first + c * 32, ep, M, N);
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + (uint32_t)(c * 32), r);
+            tmem_wait_ld();
+            if (c == NCHUNKS - 1) after_loads();
+            store_chunk(r, row, col_first + c * 32, ep, M, N, res, have_res, kv_page, kv_slot, status, bias_of(bias, c));
+        }
+        return;
+    }
+    int stores = 0;                 // TMA stores issued so far: store i uses tile i % NTILES
+    // before tile `stores % NTILES` is written again, the store that last read it must have done so
+    auto tile_free = [&] {
+        if (stores >= NTILES) {
+            if (lane == 0) {
+                if (NTILES == 1) bulk_wait_read();
+                else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            }
+            __syncwarp();
+        }
+    };
+    auto send = [&](uint8_t* tile, int col0) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // my writes, before the copy engine reads them
+        __syncwarp();
+        if (lane == 0 && col0 < N && row0 < M) store_tile(map_out, tile, col0, row0, ep.residual != nullptr);
+        else if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");     // keeps the groups counted alike
+        stores++;
+    };
+#pragma unroll 1
+    for (int c0 = 0; c0 < NCHUNKS; c0 += 2) {
+        const int col0 = col_first + c0 * 32;
+        const bool two = c0 + 1 < NCHUNKS;
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32(taddr + (uint32_t)(c0 * 32), ra);
+        if (two) tmem_ld_32x32(taddr + (uint32_t)(c0 * 32 + 32), rb);
+        tmem_wait_ld();
+        if (c0 + 2 >= NCHUNKS) after_loads();
+        if (ep.out_f32) {
+            // a float tile is one chunk wide
+            tile_free();
+            uint8_t* tile = tiles + (stores % NTILES) * EPI_WARP_BYTES;
+            stage_chunk(ra, tile, 0, row, col0, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0));
+            send(tile, col0);
+            if (two) {
+                tile_free();
+                tile = tiles + (stores % NTILES) * EPI_WARP_BYTES;
+                stage_chunk(rb, tile, 0, row, col0 + 32, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0 + 1));
+                send(tile, col0 + 32);
+            }
+        } else if (two) {
+            // a bfloat16 tile is two chunks wide
+            tile_free();
+            uint8_t* tile = tiles + (stores % NTILES) * EPI_WARP_BYTES;
+            stage_chunk(ra, tile, 0, row, col0, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0));
+            stage_chunk(rb, tile, 1, row, col0 + 32, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0 + 1));
+            send(tile, col0);
+        } else {
+            // a last bfloat16 chunk that fills only half of a tile's rows: the store would write the other
+            // half too, so this chunk goes out of the registers
+            float4 res[8];
+            store_chunk(ra, row, col0, ep, M, N, res, false, kv_page, kv_slot, status, bias_of(bias, c0));
+        }
+    }
+    if (lane == 0) bulk_wait_read();       // the staging memory may be reused (or die) after this
+    __syncwarp();
+}
+
 // ---- host side: tensor maps ------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -296,26 +484,27 @@ EncodeTiledFn get_encode_fn() {
 struct MapKey {
     const void* ptr;
     long long rows, cols, ld;
-    int box_rows;
+    int box_rows, elem;
     bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && elem == o.elem;
     }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
         size_t h = std::hash<const void*>()(k.ptr);
         h ^= std::hash<long long>()(k.rows * 1000003 + k.cols) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
-        h ^= std::hash<long long>()(k.ld * 31 + k.box_rows) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        h ^= std::hash<long long>()(k.ld * 31 + k.box_rows + 1000 * k.elem) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
         return h;
     }
 };
 
-// A 2-D bfloat16 tensor [rows, cols] with row pitch ld, cut into boxes of box_rows x 64 with
-// 128-byte swizzle.  Encoded maps are kept: a model's operands come back every step.
-bool get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+// A 2-D tensor [rows, cols] with row pitch ld (in elements) of bfloat16 (elem 2) or float (elem 4), cut
+// into boxes of box_rows x 128 bytes (64 or 32 columns) with 128-byte swizzle.  Encoded maps are kept: a
+// model's operands come back every step.
+bool get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out, int elem = 2) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows};
+    MapKey key{ptr, rows, cols, ld, box_rows, elem};
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
     if (it != cache.end()) {
@@ -325,17 +514,36 @@ bool get_map(const void* ptr, long long rows, long long cols, long long ld, int 
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return false;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * elem};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / elem), (cuuint32_t)box_rows};
+    cuuint32_t elem_strides[2] = {1, 1};
     CUtensorMap m;
-    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+    CUresult r = enc(&m, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem_strides,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return false;
     if (cache.size() > 4096) cache.clear();
     cache.emplace(key, m);
     *out = m;
+    return true;
+}
+
+// The tensor map of a product's output for the write-back through TMA, if the output allows one: a
+// 16-byte aligned base and row pitch, and no residual other than the (float) output itself.  Up to one
+// tile of rows the registers are the quicker way (a store through TMA has the longer latency, and so few
+// rows are written in no time either way: at 64 rows 5.4 us against 6.1 for a 2304 x 768 product).
+bool get_out_map(EpilogueArgs& ep, int M, int N, CUtensorMap* out) {
+    const int elem = ep.out_f32 ? 4 : 2;
+    ep.tma_out = 0;
+    memset(out, 0, sizeof(*out));
+    if (M <= BM) return false;
+    if ((reinterpret_cast<uintptr_t>(ep.out) & 15) || ((long long)ep.ldc * elem) % 16 != 0) return false;
+    // a row's end too: the store clips a row in pieces of 16 bytes (a 777-column bfloat16 output with room
+    // behind its rows had columns 777 .. 783 overwritten)
+    if (((long long)N * elem) % 16 != 0) return false;
+    if (ep.residual && (ep.residual != ep.out || ep.ldr != ep.ldc || !ep.out_f32)) return false;
+    if (!get_map(ep.out, M, N, ep.ldc, 32, out, elem)) return false;
+    ep.tma_out = 1;
     return true;
 }
 

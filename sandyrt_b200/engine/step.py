@@ -223,6 +223,12 @@ class Engine:
         if self._lib.sandy_engine_mark(ctypes.c_void_p(self._h.handle), which) != 0:
             core.raise_last_error()
 
+    def hold(self, microseconds: int) -> None:
+        """Keeps the engine's stream busy for so long (a kernel that only waits): what the host queues
+        meanwhile runs back to back behind it.  For timing the device's share of a step."""
+        if self._lib.sandy_engine_hold(ctypes.c_void_p(self._h.handle), int(microseconds)) != 0:
+            core.raise_last_error()
+
     def elapsed_ms(self) -> float:
         ms = self._lib.sandy_engine_elapsed_ms(ctypes.c_void_p(self._h.handle))
         if ms < 0:

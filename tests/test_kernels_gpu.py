@@ -135,6 +135,46 @@ def test_gemm_tc(M, N, K, tile_n):
         assert err < tol * (1 + want.abs().max().item()), (act, use_res, out_dtype, err)
 
 
+@pytest.mark.parametrize("tile_n", [0, 128, 256, -64, -128, 2128, 2256])
+@pytest.mark.parametrize("N,pitch", [(1000, 1000), (1000, 1024), (777, 777), (777, 784), (96, 4096), (40, 40)])
+def test_gemm_tc_write_back_paths(tile_n, N, pitch):
+    """Above one tile of rows the write-back goes through TMA stores where the output's rows start on
+    16-byte boundaries (a reduce-add where the residual is the output itself) and through the registers
+    where they do not; either way nothing is written outside the [M, N] window of a wider buffer, and a
+    last tile that is cut by M and by N is clipped."""
+    from sandyrt_b200.csrc import ops
+
+    M, K = 300, 200
+    a = _rand((M, K), torch.bfloat16, 1)
+    w = _rand((N, K), torch.bfloat16, 2, scale=0.1)
+    bias = _rand((N,), torch.bfloat16, 3)
+    for dtype in (torch.bfloat16, torch.float32):
+        wide = torch.full((M + 3, pitch), 7.0, dtype=dtype, device=DEV)
+        out = wide[:M, :N]
+        ops.gemm_tc(a, w, bias, out, act="gelu_new", tile_n=tile_n)
+        ops.check_kernel_status(DEV)
+        want = _gemm_want(a, w.t(), bias, "gelu_new", None)
+        tol = 1e-2 if dtype == torch.bfloat16 else 2e-5
+        assert (out.double() - want).abs().max().item() < tol * (1 + want.abs().max().item()), (dtype, "values")
+        assert bool((wide[M:] == 7.0).all()) and bool((wide[:, N:] == 7.0).all()), (dtype, "wrote outside its window")
+    # the residual stream: in place, twice over (every element receives exactly one addition a launch)
+    wide = torch.zeros(M + 3, pitch, dtype=torch.float32, device=DEV)
+    x0 = _rand((M, N), torch.float32, 4)
+    wide[:M, :N] = x0
+    x = wide[:M, :N]
+    ops.gemm_tc(a, w, bias, x, residual=x, tile_n=tile_n)
+    ops.gemm_tc(a, w, bias, x, residual=x, tile_n=tile_n)
+    ops.check_kernel_status(DEV)
+    want = x0.double() + 2 * (a.double() @ w.double().t() + bias.double())
+    assert (x.double() - want).abs().max().item() < 1e-4 * (1 + want.abs().max().item())
+    assert float(wide[M:].abs().sum()) == 0.0 and float(wide[:, N:].abs().sum()) == 0.0
+    # and the same bits whichever way the tiles are cut
+    y = x0.clone()
+    ops.gemm_tc(a, w, bias, y, residual=y, tile_n=-128)
+    ops.gemm_tc(a, w, bias, y, residual=y, tile_n=-128)
+    assert torch.equal(y, x.contiguous())
+
+
 def test_gemm_tc_in_place_residual_and_row_independence():
     """out may be the residual itself; a row's result does not depend on the rows beside it."""
     from sandyrt_b200.csrc import ops
@@ -563,6 +603,91 @@ def test_gemm_skinny_writes_keys_and_values_into_the_pages():
     target = KVTarget(arena_a[:, 0], arena_a[:, 1], table, tok_seq, tok_pos, q_cols, kv_cols, D)
     ops.gemm_skinny(a, w, bias, out_a, kv=target)
     ops.gemm_skinny(a, w, bias, out_b)
+    ops.kv_append(out_b[:, q_cols:q_cols + kv_cols], out_b[:, q_cols + kv_cols:], arena_b[:, 0], arena_b[:, 1],
+                  table, tok_seq, tok_pos)
+    ops.check_kernel_status(DEV)
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(arena_a, arena_b) and float(arena_a.abs().sum()) > 0
+
+
+@pytest.mark.parametrize("M", [1, 17, 24, 32, 33, 47, 64])
+@pytest.mark.parametrize("N,K", [(64, 64), (2304, 768), (768, 3072), (777, 240), (50257, 64), (16401, 776), (96, 320),
+                                 (1000, 96), (13, 8), (136, 1600), (520, 4104)])
+def test_gemm_small(M, N, K):
+    """The product of 17..64 rows on tcgen05 with the weight as the wide operand: one block a tile
+    and clusters of 2 to 8 blocks that split K (which of them depends on the shape), odd N, a K
+    that is no multiple of the 64-wide k-step, rows that do not fill the instruction's 64."""
+    from sandyrt_b200.csrc import ops
+
+    a = _rand((M, K), torch.bfloat16, 1)
+    w_nk = _rand((N, K), torch.bfloat16, 2, scale=0.1)
+    bias = _rand((N,), torch.bfloat16, 3)
+    res = _rand((M, N), torch.float32, 4)
+    for act, use_res, out_dtype, use_bias in ((None, False, torch.bfloat16, True), ("gelu_new", False, torch.bfloat16, True),
+                                              (None, True, torch.float32, True), (None, False, torch.float32, False)):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        ops.gemm_small(a, w_nk, bias if use_bias else None, out, act=act, residual=res if use_res else None)
+        ops.check_kernel_status(DEV)
+        want = _gemm_want(a, w_nk.t(), bias if use_bias else None, act, res if use_res else None)
+        tol = 1e-2 if out_dtype == torch.bfloat16 else 2e-5
+        err = (out.double() - want).abs().max().item()
+        assert err < tol * (1 + want.abs().max().item()), (act, use_res, out_dtype, err, ops.gemm_small_splits(N, K))
+    # in place on the residual, and the same bits every time (the blocks' sums are added in a fixed order)
+    x = res.clone()
+    ops.gemm_small(a, w_nk, None, x, residual=x)
+    assert (x.double() - (res.double() + a.double() @ w_nk.double().t())).abs().max().item() < 1e-4
+    first = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_small(a, w_nk, bias, first)
+    for _ in range(3):
+        again = torch.empty_like(first)
+        ops.gemm_small(a, w_nk, bias, again)
+        assert torch.equal(first, again)
+
+
+def test_gemm_small_splits_are_a_rule_of_the_shape():
+    from sandyrt_b200.csrc import ops
+
+    seen = {ops.gemm_small_splits(N, K) for N, K in ((2304, 768), (768, 3072), (50257, 768), (64, 64), (768, 768))}
+    assert all(1 <= s <= 8 for s in seen) and 1 in seen and max(seen) > 1
+    assert ops.gemm_small_splits(50257, 768) == 1            # more tiles than SMs: nothing to split
+    assert ops.gemm_small_splits(64, 64) == 1                # one k-step
+
+
+@pytest.mark.parametrize("H,Hkv,D,ps,K", [(6, 2, 32, 8, 96), (3, 3, 16, 16, 512), (5, 1, 48, 4, 1280)])
+def test_gemm_small_writes_keys_and_values_into_the_pages(H, Hkv, D, ps, K):
+    """The fused q/k/v product of a decode step of 17..64 requests puts its key and value columns where
+    kv_append would (split and unsplit K)."""
+    from sandyrt_b200.csrc import ops
+    from sandyrt_b200.csrc.ops import KVTarget
+
+    q_cols, kv_cols = H * D, Hkv * D
+    g = torch.Generator().manual_seed(0)
+    befores = torch.randint(0, 60, (37,), generator=g).tolist()
+    seqs = [(b, 1) for b in befores] + [(8, 3), (ps - 1, 2)]
+    T = sum(n for _, n in seqs)
+    max_blocks = -(-64 // ps)
+    num_pages = len(seqs) * max_blocks + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((len(seqs), max_blocks), -1, dtype=torch.int32)
+    tok_seq, tok_pos = [], []
+    for s, (before, n) in enumerate(seqs):
+        for b in range(-(-(before + n) // ps)):
+            table[s, b] = perm.pop()
+        tok_seq += [s] * n
+        tok_pos += list(range(before, before + n))
+    table = table.to(DEV)
+    tok_seq = torch.tensor(tok_seq, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(tok_pos, dtype=torch.int32, device=DEV)
+    a = _rand((T, K), torch.bfloat16, 1)
+    w = _rand((q_cols + 2 * kv_cols, K), torch.bfloat16, 2, scale=0.2)
+    bias = _rand((q_cols + 2 * kv_cols,), torch.bfloat16, 3)
+    arena_a = torch.zeros(num_pages, 2, Hkv, ps, D, dtype=torch.bfloat16, device=DEV)
+    arena_b = torch.zeros_like(arena_a)
+    out_a = torch.empty(T, q_cols + 2 * kv_cols, dtype=torch.bfloat16, device=DEV)
+    out_b = torch.empty_like(out_a)
+    target = KVTarget(arena_a[:, 0], arena_a[:, 1], table, tok_seq, tok_pos, q_cols, kv_cols, D)
+    ops.gemm_small(a, w, bias, out_a, kv=target)
+    ops.gemm_small(a, w, bias, out_b)
     ops.kv_append(out_b[:, q_cols:q_cols + kv_cols], out_b[:, q_cols + kv_cols:], arena_b[:, 0], arena_b[:, 1],
                   table, tok_seq, tok_pos)
     ops.check_kernel_status(DEV)
