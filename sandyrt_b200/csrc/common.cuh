@@ -99,6 +99,12 @@ static inline int sandy_sm_count() {
 // pdl_wait() returns when the predecessor has completed and its writes are visible.  What may
 // go before pdl_wait() is work on data no kernel writes: index arithmetic and, above all, the
 // first loads of the weights.  Both calls do nothing in a kernel launched the ordinary way.
+//
+// What earlier STEPS wrote may also be read before pdl_wait() -- cache pages of older positions, the
+// step's index arrays (a burst's sampler advances them at the end of the step before) -- because a
+// step's first kernel (the embedding) calls pdl_launch_dependents() only after its own pdl_wait() has
+// returned: no later kernel of the step can start before that, and by then every kernel of the steps
+// before has completed (a kernel completes only after its wait, which needs its predecessor complete).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

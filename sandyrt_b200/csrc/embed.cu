@@ -15,8 +15,11 @@ __global__ void embed_pos_kernel(const int* __restrict__ ids, const int* __restr
                                  const TT* __restrict__ wte, const TT* __restrict__ wpe,
                                  TO* __restrict__ out, int width, int vocab, int n_pos,
                                  int* __restrict__ status) {
-    pdl_launch_dependents();
+    // The first kernel of a step lets its successors start only after its own wait has returned: by then
+    // every kernel of the steps before has completed, so the step's later kernels may read what those steps
+    // wrote (cache pages of older positions, the index arrays) before their own waits.
     pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int id = ids[t];
     const int p = wpe ? pos[t] : 0;
