@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload medium|xl          the mixed-batch workloads through LLM.generate
     python bench.py --profile-kernels             time per kernel class of a decode and a prompt step
+    python bench.py --attribute [--batch B]       what each family of launches costs inside a step (leave-one-out)
     python bench.py --micro gemm|decode-attention|prefill-attention [...]   kernel micro-benchmarks
 
 Default workload: GPT-2 small (12 layers, width 768, 12 heads of 64, inner 3072, vocabulary 50257,
@@ -310,6 +311,46 @@ def workload(name: str, dtype_name: str, layers: int) -> int:
     return 0
 
 
+def attribute(dtype_name: str, layers: int, batch: int) -> int:
+    """What each family of launches costs INSIDE a step: the step is timed whole and again with the
+    family left out (its results are garbage then; only the time is read), and the difference is the
+    family's share with all overlap between neighbouring kernels as it is in the real step.  A decode
+    step of `batch` requests at the bench's context and a prompt step of 2 x 1,024 tokens."""
+    import numpy as np
+
+    from sandyrt_b200 import core
+    from sandyrt_b200.engine.llm import LLM
+
+    raw = load_model_config("small")
+    from sandyrt_b200.config.gpt2 import GPT2Config
+    cfg = GPT2Config.from_dict(raw)
+    E, I, V = cfg.n_embd, cfg.inner_dim, cfg.vocab_size
+    cases = [("nothing", []), ("layernorm (own launches)", ["layernorm"]), ("attention", ["attention"]),
+             (f"q/k/v projection {3 * E}x{E}", [f"product {3 * E}x{E}"]), (f"out-projection {E}x{E}", [f"product {E}x{E}"]),
+             (f"up-projection {I}x{E}", [f"product {I}x{E}"]), (f"down-projection {E}x{I}", [f"product {E}x{I}"]),
+             (f"vocabulary {V}x{E}", [f"product {V}x{E}"]),
+             ("all of these", ["layernorm", "attention", "product"])]
+    rows = []
+    for name, families in cases:
+        model, cfg = make_model(raw, layers or raw["n_layer"], dtype_name)     # an LLM takes its model over
+        core.call("global", None, "leave_out", families=families)
+        try:
+            rng = np.random.default_rng(0)
+            llm = LLM(model, cache_tokens=64 * 1024 + 4096, max_live=64, max_step_tokens=4096, prefill_chunk_tokens=2048)
+            d_ms, _, ctx, launches = decode_run(llm, batch, 128, 24, 3, rng, V, want_e2e=False)
+            p_ms, _ = prefill_run(llm.engine, V, rng, reps=3)
+        finally:
+            core.call("global", None, "leave_out", families=[])
+        rows.append((name, d_ms * 1e3, launches, p_ms * 1e3))
+        del llm, model
+    d0, p0 = rows[0][1], rows[0][3]
+    print(f"{dtype_name}, {cfg.n_layer} layers; decode step of {batch} requests at context ~{ctx:.0f}, prompt step of 2 x 1,024 tokens")
+    print(f"  {'left out':32s} {'decode us':>10s} {'saves':>8s} {'per layer':>10s} {'launches':>9s} {'prompt us':>10s} {'saves':>8s} {'per layer':>10s}")
+    for name, d, launches, p in rows:
+        print(f"  {name:32s} {d:10.1f} {d0 - d:8.1f} {(d0 - d) / cfg.n_layer:10.2f} {launches:9d} {p:10.1f} {p0 - p:8.1f} {(p0 - p) / cfg.n_layer:10.2f}")
+    return 0
+
+
 def profile_kernels(dtype_name: str, layers: int, batch: int) -> int:
     """Device time per kernel class of one decode step and one 2,048-token prompt step (eager
     launches with a pair of CUDA events around each, so launch gaps are not in the figures)."""
@@ -366,6 +407,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the float32 block")
     ap.add_argument("--workload", choices=["medium", "xl"], help="run a mixed-batch workload through LLM.generate instead")
     ap.add_argument("--profile-kernels", action="store_true", help="print device time per kernel class instead")
+    ap.add_argument("--attribute", action="store_true", help="print what each family of launches costs inside a step instead")
     ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -380,6 +422,8 @@ def main() -> int:
         return workload(args.workload, args.dtype, args.layers)
     if args.profile_kernels:
         return profile_kernels(args.dtype, args.layers, args.batch)
+    if args.attribute:
+        return attribute(args.dtype, args.layers, args.batch)
     if args.warmup < 3:
         args.warmup = 3
 

@@ -291,6 +291,13 @@ Json call_global(const std::string& m, const Json& a) {
     }
     if (m == "decode_splits")
         return Json(ops::decode_splits((int)a.at("n_tokens").as_int(), (int)a.at("n_heads").as_int(), (int)a.at("max_kv").as_int(), (int)geti(a, "sms", 0)));
+    if (m == "leave_out") {                           // {"families": [...]}: launches to skip (timing only); [] restores
+        std::vector<std::string> families;
+        if (a.has("families"))
+            for (const Json& f : a.at("families").items()) families.push_back(f.as_string());
+        ops::leave_out(families);
+        return Json();
+    }
     if (m == "profile_kernels") {                     // {"enable": bool} -> what was gathered since it was switched on
         Json out = Json::array();
         for (const ops::ProfileRow& r : ops::profile_report()) {

@@ -68,6 +68,24 @@ private:
     bool on_ = false;
 };
 
+// ---- leaving launches out -------------------------------------------------------------------------
+// What a kernel costs inside a step -- where its set-up runs under the tail of the kernel before and the
+// next one's under its own -- is not what it takes when timed alone.  For that figure a step is timed with
+// a family of launches left out (its results are then garbage; only the time is read) and the difference
+// to the whole step taken: families "layernorm", "attention", "kv_append", and "product" or
+// "product <N>x<K>" for the products of one shape.  Set through the control plane (leave_out); graphs
+// recorded before a change still hold the launches, so a fresh engine is made for every setting.
+std::vector<std::string> g_left_out;
+
+bool left_out(const char* family, int64_t N = 0, int64_t K = 0) {
+    if (g_left_out.empty()) return false;
+    const std::string f = family;
+    const std::string shaped = N ? f + " " + std::to_string(N) + "x" + std::to_string(K) : f;
+    for (const std::string& x : g_left_out)
+        if (x == f || x == shaped) return true;
+    return false;
+}
+
 double tensor_bytes(const Tensor* t) { return t ? (double)t->numel() * (double)t->elem_size() : 0.0; }
 
 std::string dims(const Tensor& t) { return "[" + std::to_string(t.rows) + ", " + std::to_string(t.cols) + "]"; }
@@ -87,6 +105,8 @@ const char* kernel_status_text() {
 }
 
 void profile_enable(bool on) { g_profile = on; }
+
+void leave_out(const std::vector<std::string>& families) { g_left_out = families; }
 
 std::vector<ProfileRow> profile_report() {
     std::map<std::string, ProfileRow> by_class;
@@ -139,6 +159,7 @@ void layernorm(const Launch& l, const Tensor& x, const Tensor& gamma, const Tens
     if (!rows && x.rows < n_rows) throw KernelError("layernorm: x and out disagree");
     if (!x.contiguous() || !out.contiguous() || out.cols != width || gamma.numel() != width || out.rows < n_rows)
         throw KernelError("layernorm: contiguous [rows, width] tensors expected");
+    if (left_out("layernorm")) return;
     static auto fn = SANDY_KERNEL(norm, sandy_layernorm);
     OpTimer timer(l, "layernorm", (double)n_rows * width * (x.elem_size() + out.elem_size()), 0);
     check(fn(x.data, gamma.data, beta ? beta->data : nullptr, out.data, rows, n_rows, (int)width, eps, code_of(x.dtype),
@@ -228,6 +249,10 @@ void gemm_tc(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bi
             kv->q_cols + 2 * kv->kv_cols != N)
             throw KernelError("gemm_tc: the key/value target does not match the product");
     }
+    if (left_out("product", N, K)) {
+        if (kv) kv->written = true;
+        return;
+    }
     OpTimer timer(l, kv ? "product, tcgen05 (+ cache write)" : "product, tcgen05",
                   tensor_bytes(&a) + tensor_bytes(&w) + tensor_bytes(&out) + 2 * tensor_bytes(residual), 2.0 * M * N * K);
     const TcArgs g{&a, &w, bias, act, M, N, K};
@@ -304,6 +329,10 @@ void gemm_skinny(const Launch& l, const Tensor* a, const FusedNorm* norm, const 
     if (kv && (c->dtype != DType::BF16 || out.dtype != DType::BF16 || kv->kv_cols != c->n_kv_heads * c->head_dim ||
                kv->q_cols + 2 * kv->kv_cols != N))
         throw KernelError("gemm_skinny: the key/value target does not match the product");
+    if (left_out("product", N, K)) {
+        if (kv) kv->written = true;
+        return;
+    }
     static auto fn = SANDY_KERNEL(gemm_skinny, sandy_gemm_skinny);
     OpTimer timer(l, norm ? (kv ? "product, streaming (+ norm, cache write)" : "product, streaming (+ norm)") : "product, streaming",
                   (norm ? tensor_bytes(&norm->x) : tensor_bytes(a)) + tensor_bytes(&w) + tensor_bytes(&out) + 2 * tensor_bytes(residual),
@@ -355,6 +384,10 @@ void gemm_small(const Launch& l, const Tensor& a, const Tensor& w, const Tensor*
     if (kv && (c->dtype != DType::BF16 || out.dtype != DType::BF16 || kv->kv_cols != c->n_kv_heads * c->head_dim ||
                kv->q_cols + 2 * kv->kv_cols != N))
         throw KernelError("gemm_small: the key/value target does not match the product");
+    if (left_out("product", N, K)) {
+        if (kv) kv->written = true;
+        return;
+    }
     static auto fn = SANDY_KERNEL(gemm_small, sandy_gemm_small);
     OpTimer timer(l, kv ? "product, tcgen05 split-K (+ cache write)" : "product, tcgen05 split-K",
                   tensor_bytes(&a) + tensor_bytes(&w) + tensor_bytes(&out) + 2 * tensor_bytes(residual), 2.0 * M * N * K);
@@ -373,6 +406,7 @@ void kv_append(const Launch& l, const Tensor& k_src, const Tensor& v_src, const 
     if (k_src.rows != v_src.rows || k_src.cols != v_src.cols || k_src.cols != (int64_t)c.n_kv_heads * c.head_dim ||
         k_src.ld != v_src.ld || k_src.dtype != c.dtype || v_src.dtype != c.dtype)
         throw KernelError("kv_append: sources must be [T, Hkv*D] of the cache's dtype with one stride");
+    if (left_out("kv_append")) return;
     static auto fn = SANDY_KERNEL(attention, sandy_kv_append);
     OpTimer timer(l, "key/value append", 2 * (tensor_bytes(&k_src) + tensor_bytes(&v_src)), 0);
     check(fn(k_src.data, v_src.data, (int)k_src.ld, c.k, c.v, c.page_stride, block_table, max_blocks, token_seq, positions,
@@ -419,6 +453,7 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     if (q.cols != (int64_t)n_heads * d || out.rows != q.rows || out.cols != q.cols || q.dtype != c.dtype || out.dtype != q.dtype)
         throw KernelError("attention: q and out must be [T, H*D] of the cache's dtype");
     const int T = (int)q.rows;
+    if (left_out("attention")) return;
     const double attn_bytes = 2.0 * s.kv_tokens * hkv * d * q.elem_size() + 2 * tensor_bytes(&q);
     const double attn_flops = 4.0 * s.pairs * n_heads * d;
     const std::string shape = "(H=" + std::to_string(n_heads) + ",Hkv=" + std::to_string(hkv) + ",D=" + std::to_string(d) + ")";

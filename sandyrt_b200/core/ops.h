@@ -39,6 +39,9 @@ struct ProfileRow {
     double us = 0, bytes = 0, flops = 0;
 };
 void profile_enable(bool on);
+// Families of launches that are skipped from now on ("layernorm", "attention", "kv_append", "product",
+// "product <N>x<K>"): for timing what a family costs inside a step; results are garbage meanwhile.
+void leave_out(const std::vector<std::string>& families);
 std::vector<ProfileRow> profile_report();              // also clears what was gathered
 
 int sm_count();                                        // streaming multiprocessors of the current device

@@ -115,8 +115,11 @@ decode_attention_bulk_kernel(const T* __restrict__ q, int ld_q, const T* __restr
     __shared__ float sm_o[GROUPS][D];
     __shared__ float cl_o[D], cl_ml[2];
 
+    // The kernel before this one writes the query and the token's own key and value; the index arrays and
+    // the pages of older positions were written by earlier steps (complete by now, see common.cuh).  So the
+    // producer starts filling the ring at once and waits for that kernel only in front of the page that
+    // holds the token's own position; the consumers wait before they read the query.
     pdl_launch_dependents();
-    pdl_wait();
     const int split = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int s = token_seq[t];
@@ -151,6 +154,8 @@ decode_attention_bulk_kernel(const T* __restrict__ q, int ld_q, const T* __restr
         // already on their way); lane 0 then feeds the ring.
         auto entry = [&](int i) { return (i < n_pages && p0 + i < max_blocks) ? __ldg(table + p0 + i) : -1; };
         bool failed = false;
+        const int own_page = (pos >> page_shift) - p0;       // the page the kernel before is still writing to
+        bool waited = false;
         int mine = entry(lane);
         for (int c = 0; c < n_pages; c += 32) {
             const int ahead = entry(c + 32 + lane);
@@ -159,6 +164,10 @@ decode_attention_bulk_kernel(const T* __restrict__ q, int ld_q, const T* __restr
                 const int page = __shfl_sync(0xffffffffu, mine, jj);
                 if (lane != 0 || failed) continue;
                 const int i = c + jj;
+                if (i >= own_page && !waited) {
+                    pdl_wait();
+                    waited = true;
+                }
                 const int st = i % n_stages;
                 if (i >= n_stages && !mbar_wait(&empty_bar[st], ((i / n_stages) - 1) & 1)) {
                     if (status) atomicOr(status, 32);
@@ -181,8 +190,10 @@ decode_attention_bulk_kernel(const T* __restrict__ q, int ld_q, const T* __restr
             }
             mine = ahead;
         }
+        pdl_wait();       // every thread has waited before the block writes its output (a second wait returns at once)
     } else {
         // ---------------- consumers ----------------
+        pdl_wait();
         const int g = lane / LPK, sub = lane % LPK;
         const int group = warp * KPW + g;
         // Which pieces this lane takes.  Lane groups of odd index start with the upper half of

@@ -87,7 +87,7 @@ class LLM:
                     prefill_chunk_tokens=prefill_chunk_tokens, eos_token_ids=[int(t) for t in (eos_token_ids or ())],
                     max_context_tokens=max_context_tokens, use_cuda_graphs=use_cuda_graphs, max_burst=max_burst,
                     pipeline_bursts=pipeline_bursts)
-        h = self._lib.sandy_llm_from_model(ctypes.c_void_p(self.model._h.handle), json.dumps(opts).encode())
+        h = self._lib.sandy_llm_from_model(ctypes.c_void_p(self.model._handle_for_engine()), json.dumps(opts).encode())
         if not h:
             core.raise_last_error()
         self._h = core.Handle("llm", h)              # the library's LLM now owns the model

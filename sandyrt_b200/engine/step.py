@@ -106,7 +106,7 @@ class Engine:
         self.model = model
         if _handle is None:
             _handle = core.Handle("engine", core.call(
-                "global", None, "new_engine", model=model._h.handle, max_tokens=int(max_tokens), page_size=page_size,
+                "global", None, "new_engine", model=model._handle_for_engine(), max_tokens=int(max_tokens), page_size=page_size,
                 max_requests=max_requests, max_step_tokens=max_step_tokens, use_cuda_graphs=use_cuda_graphs)["handle"],
                 keep=model._h)
         self._h = _handle

@@ -39,6 +39,13 @@ class Model:
     def _info(self):
         return self._h.call(self._info_method)
 
+    def _handle_for_engine(self) -> int:
+        """The library's model object, to hand to an engine; a model that an LLM has taken over is
+        not one any more."""
+        if self._h.kind != "model":
+            raise ValueError("this model already belongs to an LLM: build or load another one for a second engine")
+        return self._h.handle
+
     def _moved_into(self, owner: core.Handle) -> None:
         """An engine of the library has taken the model over: ask it from now on."""
         self._h = core.Handle(owner.kind, owner.handle, owned=False, keep=owner)

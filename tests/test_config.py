@@ -92,3 +92,16 @@ def test_model_description_is_data(model_dirs):
     assert req["h.2.mlp.c_proj.weight"].shape == (320, 96)
     assert req["wte.weight"].shape == (1000, 96) and req["wpe.weight"].shape == (256, 96)
     assert "lm_head.weight" not in req      # tied
+
+
+def test_a_model_an_llm_has_taken_over_cannot_be_handed_to_a_second_engine():
+    """LLM() takes its model over; passing the same Model object again raises (it used to crash)."""
+    import sandyrt_b200.core as core
+    from sandyrt_b200.models.model import Model
+
+    m = Model.__new__(Model)
+    m._h = core.Handle("llm", 0, owned=False)
+    with pytest.raises(ValueError, match="already belongs"):
+        m._handle_for_engine()
+    m._h = core.Handle("model", 1234, owned=False)
+    assert m._handle_for_engine() == 1234
