@@ -407,6 +407,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the float32 block")
     ap.add_argument("--workload", choices=["medium", "xl"], help="run a mixed-batch workload through LLM.generate instead")
     ap.add_argument("--profile-kernels", action="store_true", help="print device time per kernel class instead")
+    ap.add_argument("--under-profiler", action="store_true",
+                    help="skip the check of the device time against the wall clock (a profiler serialises the launches)")
     ap.add_argument("--attribute", action="store_true", help="print what each family of launches costs inside a step instead")
     ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
@@ -445,7 +447,7 @@ def main() -> int:
     # ---- decode at the headline batch ------------------------------------------------------------
     dev_ms, (wall_ms, e2e_h2d, e2e_d2h), mean_ctx, launches_per_step = decode_run(
         llm, args.batch, args.prompt_len, args.steps, args.warmup, rng, vocab)
-    if dev_ms > wall_ms * 1.05:
+    if dev_ms > wall_ms * 1.05 and not args.under_profiler:
         raise RuntimeError(f"device time {dev_ms:.4f} ms a step exceeds the wall-clock {wall_ms:.4f} ms of the same work")
     value = args.batch / (dev_ms / 1e3)
     e2e_value = args.batch / (wall_ms / 1e3)
