@@ -244,9 +244,11 @@ def prefill_run(engine, vocab, rng, n_prompts=2, prompt_len=1024, reps=5, hold_u
     the host prepares and queues the step, so the step's copy and kernels run back to back behind it and
     the events bracket them alone.  with_host_ms: the same step timed from the moment the host starts on
     it with an idle device, preparation and launch latency included."""
+    import numpy as np
+
     from sandyrt_b200.engine.step import StepEntry
 
-    prompts = [rng.integers(0, vocab, size=prompt_len).tolist() for _ in range(n_prompts)]
+    prompts = [rng.integers(0, vocab, size=prompt_len, dtype=np.int32) for _ in range(n_prompts)]
     device, with_host = [], []
     for it in range(3 + 2 * reps):
         entries = [StepEntry(f"p{it}-{i}", p, [len(p) - 1]) for i, p in enumerate(prompts)]

@@ -113,6 +113,7 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     __shared__ float sm_o[GROUPS][D];
     __shared__ float cl_all[MAX_CLUSTER_SPLITS][D + 2];   // in the cluster's first block: every split's (output, max, sum)
     __shared__ __align__(16) uint8_t st_k[STAGE_KEYS * ROW_BYTES], st_v[STAGE_KEYS * ROW_BYTES];
+    __shared__ uint8_t st_ok[STAGE_KEYS];       // whether a staged key had a page behind it
 
     pdl_launch_dependents();
     const bool in_cluster = num_splits > 1 && partial_o == nullptr;
@@ -143,13 +144,19 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     for (int j = begin + group; j < stage_end; j += GROUPS) {
         const int b = j / page_size;
         const int page = b < max_blocks ? table[b] : -1;
-        if (page >= 0 && page < num_pages) {
+        const bool ok = page >= 0 && page < num_pages;
+        if (ok) {
             const size_t off = (size_t)page * page_stride + ((size_t)kvh * page_size + (j % page_size)) * D + sub * VEC;
             copy16_async(st_k + (j - begin) * ROW_BYTES + sub * 16, k_cache + off);
             copy16_async(st_v + (j - begin) * ROW_BYTES + sub * 16, v_cache + off);
         }
+        if (sub == 0) st_ok[j - begin] = ok ? 1 : 0;     // read back by this group's lanes only
     }
+    __syncwarp();                                          // ... which are lanes of this warp
     asm volatile("cp.async.commit_group;" ::: "memory");
+    // the page of the token's own position too: its table entry is the step's input like the others
+    const int own_b = pos / page_size;
+    const int own_page = (pos >= begin && pos < end && own_b < max_blocks) ? table[own_b] : -1;
     pdl_wait();
 
     float qf[VEC];
@@ -171,8 +178,15 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
             const int j = base + g + u * GROUPS;
             ok[u] = j < end;
             if (ok[u]) {
-                const int b = j / page_size;
-                const int page = b < max_blocks ? table[b] : -1;
+                // staged keys carry their answer; the token's own page was looked up before the wait; only a
+                // range too long for the staging area walks the table here
+                int page;
+                if (j < stage_end) page = st_ok[j - begin] ? 0 : -1;
+                else if (j == pos) page = own_page;
+                else {
+                    const int b = j / page_size;
+                    page = b < max_blocks ? table[b] : -1;
+                }
                 if (page < 0 || page >= num_pages) {
                     if (status && sub == 0) atomicOr(status, 16);   // a visible key with no page behind it
                     ok[u] = false;

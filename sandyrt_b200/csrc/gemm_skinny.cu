@@ -146,6 +146,20 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
     const int my_col = n0 + (int)(threadIdx.x % COLS);
     const float my_bias = (bias && my_col < N) ? __bfloat162float(bias[my_col]) : 0.0f;
 
+    // The page this thread's key/value element goes to: two dependent loads, needed only in the
+    // write-back.  The index arrays are the step's input (written before the step, or by the sampler of
+    // the step before in a burst; complete by now, see common.cuh), so the loads go out before the wait:
+    // behind it they were a trip to memory between the wait and the norm.
+    int kv_page = -1, kv_pos = 0;
+    if (kv.k_cache && MT == 1 && threadIdx.x < 16 * COLS) {
+        const int m = threadIdx.x / COLS;
+        if (m < M && n0 + (int)(threadIdx.x % COLS) >= kv.q_cols) {
+            kv_pos = kv.positions[m];
+            const int b = kv_pos / kv.page_size;
+            kv_page = (kv_pos >= 0 && b < kv.max_blocks) ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
+        }
+    }
+
     // Everything above touched only weights, which no kernel writes.  From here on the
     // activations are read: the kernels before this one must have finished.
     pdl_launch_dependents();
@@ -158,17 +172,6 @@ gemm_skinny_kernel(const bf16* __restrict__ a, NormArgs norm, const bf16* __rest
     if (MT == 1 && residual && threadIdx.x < 16 * COLS && (int)(threadIdx.x / COLS) < M && my_col < N)
         my_res = residual[(size_t)(threadIdx.x / COLS) * ldr + my_col];
 
-    // The page this thread's key/value element goes to (two dependent loads): asked for now,
-    // needed only in the write-back.
-    int kv_page = -1, kv_pos = 0;
-    if (kv.k_cache && MT == 1 && threadIdx.x < 16 * COLS) {
-        const int m = threadIdx.x / COLS;
-        if (m < M && n0 + (int)(threadIdx.x % COLS) >= kv.q_cols) {
-            kv_pos = kv.positions[m];
-            const int b = kv_pos / kv.page_size;
-            kv_page = (kv_pos >= 0 && b < kv.max_blocks) ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
-        }
-    }
 
     if (FUSE_LN) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");

@@ -19,6 +19,8 @@ the drawn tokens back.
 from __future__ import annotations
 
 import ctypes
+
+import numpy as np
 import dataclasses
 import json
 from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple, Union
@@ -119,10 +121,13 @@ class LLM:
         self._next_id += 1
         if rid in self._lib_id:
             raise RequestRefused(f"request id {rid!r} is in use")
-        prompt = [int(t) for t in prompt_ids]
+        prompt = np.ascontiguousarray(np.asarray(prompt_ids, dtype=np.int64).reshape(-1).astype(np.int32))
+        n_prompt = int(prompt.size)
+        if n_prompt == 0:
+            prompt = np.zeros(1, dtype=np.int32)
         stop = [int(s) for s in stop_token_ids]
         i = self._lib.sandy_llm_add_request(
-            ctypes.c_void_p(self._h.handle), (ctypes.c_int * max(len(prompt), 1))(*prompt), len(prompt), int(max_tokens),
+            ctypes.c_void_p(self._h.handle), prompt.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), n_prompt, int(max_tokens),
             ctypes.c_float(sp.temperature), int(sp.top_k), ctypes.c_float(sp.top_p), 0 if sp.seed is None else 1,
             ctypes.c_ulonglong((sp.seed or 0) & ((1 << 64) - 1)), (ctypes.c_int * max(len(stop), 1))(*stop), len(stop))
         if i < 0:

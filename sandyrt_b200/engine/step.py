@@ -97,6 +97,16 @@ def _ints(values) -> "ctypes.Array":
     return (ctypes.c_int * max(len(values), 1))(*values)
 
 
+def _int_array(parts) -> np.ndarray:
+    """The concatenation of integer sequences (lists or arrays) as one contiguous int32 array: for the
+    token ids of a step, which may be thousands (a ctypes array built from a list costs ten times this)."""
+    arrays = [np.asarray(p, dtype=np.int32).reshape(-1) for p in parts]
+    if not arrays:
+        return np.zeros(1, dtype=np.int32)
+    out = arrays[0] if len(arrays) == 1 else np.concatenate(arrays)
+    return np.ascontiguousarray(out) if out.size else np.zeros(1, dtype=np.int32)
+
+
 class Engine:
     """A bound model, its cache and the step function over them."""
 
@@ -154,7 +164,7 @@ class Engine:
         wanted place) the drawn tokens are read with `read_sampled(n)` afterwards."""
         n = len(entries)
         rids = (ctypes.c_longlong * max(n, 1))(*[self.ids.of(e.rid) for e in entries])
-        tokens = [int(t) for e in entries for t in e.tokens]
+        tokens = _int_array([e.tokens for e in entries])
         want = [int(w) for e in entries for w in e.want]
         samp = None
         if sampling is not None:
@@ -162,7 +172,8 @@ class Engine:
             samp = (ctypes.c_float * max(len(flat), 1))(*flat)
         logits, rows, cols = ctypes.c_void_p(), ctypes.c_int(), ctypes.c_int()
         code = self._lib.sandy_engine_step(ctypes.c_void_p(self._h.handle), n, rids, _ints([len(e.tokens) for e in entries]),
-                                           _ints(tokens), _ints([len(e.want) for e in entries]), _ints(want), samp,
+                                           tokens.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
+                                           _ints([len(e.want) for e in entries]), _ints(want), samp,
                                            ctypes.byref(logits), ctypes.byref(rows), ctypes.byref(cols))
         if code != 0:
             core.raise_last_error()
