@@ -203,25 +203,38 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
                 }
             }
         }
+        // The round's scores first (independent of one another), then ONE new maximum and one correction for
+        // the round, then the round's exponentials: a key's update no longer waits for the key before it.
+        float sc[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
-            float sc = 0.0f;
+            float d = 0.0f;
             if (ok[u]) {
 #pragma unroll
-                for (int i = 0; i < VEC; i++) sc = fmaf(qf[i], kf[u][i], sc);
+                for (int i = 0; i < VEC; i++) d = fmaf(qf[i], kf[u][i], d);
             }
 #pragma unroll
-            for (int w = LPK / 2; w > 0; w >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, w);
-            if (ok[u]) {          // uniform across the LPK lanes of the group
-                sc *= scale;
-                const float m_new = fmaxf(m, sc);
-                const float corr = expf(m - m_new);
-                const float p = expf(sc - m_new);
-                l = l * corr + p;
+            for (int w = LPK / 2; w > 0; w >>= 1) d += __shfl_xor_sync(0xffffffffu, d, w);
+            sc[u] = ok[u] ? d * scale : -INFINITY;          // ok[u] is uniform across the LPK lanes of the group
+        }
+        float m_new = m;
 #pragma unroll
-                for (int i = 0; i < VEC; i++) o[i] = fmaf(p, vf[u][i], o[i] * corr);
-                m = m_new;
+        for (int u = 0; u < UNROLL; u++) m_new = fmaxf(m_new, sc[u]);
+        if (m_new > -INFINITY) {
+            const float corr = expf(m - m_new);              // exp(-inf) = 0 while nothing has been seen yet
+            l *= corr;
+#pragma unroll
+            for (int i = 0; i < VEC; i++) o[i] *= corr;
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                if (ok[u]) {
+                    const float p = expf(sc[u] - m_new);
+                    l += p;
+#pragma unroll
+                    for (int i = 0; i < VEC; i++) o[i] = fmaf(p, vf[u][i], o[i]);
+                }
             }
+            m = m_new;
         }
     }
 
