@@ -58,28 +58,94 @@ __device__ __forceinline__ float ld_peer(uint32_t addr, uint32_t rank) {
     return v;
 }
 
-// One output element: bias, activation, cache write, residual, store.
-__device__ __forceinline__ void finish(float acc, int m, int n, float bias, const EpilogueArgs& ep, int N,
-                                       const int* kv_page, const int* kv_slot, int* status) {
+// What the write-back needs of the epilogue arguments, read once into registers.  (Handing the kernel's
+// parameter struct itself to the per-element function made every element's field reads slow: a 64 x 16384
+// product took 16 us with it and 4.3 with these scalars.)
+struct Finish {
+    const float* residual;
+    void* out;
+    int ldr, ldc, act, out_f32;
+    bf16* k_cache;
+    bf16* v_cache;
+    long long page_stride;
+    int q_cols, kv_cols, head_dim, page_size, num_pages;
+};
+
+__device__ __forceinline__ Finish make_finish(const EpilogueArgs& ep) {
+    Finish f;
+    f.residual = ep.residual; f.out = ep.out; f.ldr = ep.ldr; f.ldc = ep.ldc; f.act = ep.act; f.out_f32 = ep.out_f32;
+    f.k_cache = ep.kv.k_cache; f.v_cache = ep.kv.v_cache; f.page_stride = ep.kv.page_stride;
+    f.q_cols = ep.kv.q_cols; f.kv_cols = ep.kv.kv_cols; f.head_dim = ep.kv.head_dim; f.page_size = ep.kv.page_size;
+    f.num_pages = ep.kv.num_pages;
+    return f;
+}
+
+// One output element: bias, activation, cache write, residual, store.  What the product has of these is a
+// template argument: chosen per element at run time, the compiler computed every activation and the cache
+// address with its divisions for every element and then picked (a 64 x 16384 product with none of them:
+// 16 us, of which 12 went there).
+template <int ACT, bool KV, bool RES, bool F32>
+__device__ __forceinline__ void finish(float acc, int m, int n, float bias, const Finish& f, int N, const int* kv_page,
+                                       const int* kv_slot, int* status) {
     if (n >= N) return;
-    float v = apply_act_fast(acc + bias, ep.act);
-    if (ep.kv.k_cache && n >= ep.kv.q_cols) {
-        const int page = kv_page[m];
-        if (page < 0 || page >= ep.kv.num_pages) {
-            if (status) atomicOr(status, 8);                 // a key/value write with no page behind it
-        } else {
-            const int c = n - ep.kv.q_cols;
-            const bool is_v = c >= ep.kv.kv_cols;
-            const int c2 = is_v ? c - ep.kv.kv_cols : c;
-            const int head = c2 / ep.kv.head_dim, d = c2 % ep.kv.head_dim;
-            (is_v ? ep.kv.v_cache : ep.kv.k_cache)[(size_t)page * ep.kv.page_stride +
-                                                  ((size_t)head * ep.kv.page_size + kv_slot[m]) * ep.kv.head_dim + d] =
-                __float2bfloat16_rn(v);
+    float v = acc + bias;
+    if (ACT == SANDY_ACT_GELU_TANH) v = gelu_tanh_fast(v);
+    if (ACT == SANDY_ACT_GELU_ERF) v = gelu_erf(v);
+    if (KV) {
+        if (n >= f.q_cols) {
+            const int page = kv_page[m];
+            if (page < 0 || page >= f.num_pages) {
+                if (status) atomicOr(status, 8);                 // a key/value write with no page behind it
+            } else {
+                const int c = n - f.q_cols;
+                const bool is_v = c >= f.kv_cols;
+                const int c2 = is_v ? c - f.kv_cols : c;
+                const int head = c2 / f.head_dim, d = c2 % f.head_dim;
+                (is_v ? f.v_cache : f.k_cache)[(size_t)page * f.page_stride + ((size_t)head * f.page_size + kv_slot[m]) * f.head_dim + d] =
+                    __float2bfloat16_rn(v);
+            }
         }
     }
-    if (ep.residual) v += ep.residual[(size_t)m * ep.ldr + n];
-    if (ep.out_f32) reinterpret_cast<float*>(ep.out)[(size_t)m * ep.ldc + n] = v;
-    else reinterpret_cast<bf16*>(ep.out)[(size_t)m * ep.ldc + n] = __float2bfloat16_rn(v);
+    if (RES) v += f.residual[(size_t)m * f.ldr + n];
+    if (F32) reinterpret_cast<float*>(f.out)[(size_t)m * f.ldc + n] = v;
+    else reinterpret_cast<bf16*>(f.out)[(size_t)m * f.ldc + n] = __float2bfloat16_rn(v);
+}
+
+// The write-back of one thread's column: `count` tokens from token m0 in steps of `step`, their sums given by
+// value(i).  One instance per combination of epilogue features that occurs; the choice is made once, out here.
+// FIXED > 0: the loop is unrolled FIXED times with `count` as a predicate (value(i) may then index registers).
+template <int ACT, bool KV, bool RES, bool F32, int FIXED, typename Value>
+__device__ __forceinline__ void finish_column(int m0, int step, int count, int n, float bias, const Finish& f, int N,
+                                              const int* kv_page, const int* kv_slot, int* status, Value value) {
+    if (FIXED > 0) {
+#pragma unroll
+        for (int i = 0; i < FIXED; i++)
+            if (i < count) finish<ACT, KV, RES, F32>(value(i), m0 + i * step, n, bias, f, N, kv_page, kv_slot, status);
+    } else {
+#pragma unroll 2
+        for (int i = 0; i < count; i++) finish<ACT, KV, RES, F32>(value(i), m0 + i * step, n, bias, f, N, kv_page, kv_slot, status);
+    }
+}
+
+template <int FIXED, typename Value>
+__device__ __forceinline__ void finish_dispatch(int m0, int step, int count, int n, float bias, const Finish& f, int N,
+                                                const int* kv_page, const int* kv_slot, int* status, Value value) {
+#define SANDY_FINISH(ACT, KV, RES, F32) finish_column<ACT, KV, RES, F32, FIXED>(m0, step, count, n, bias, f, N, kv_page, kv_slot, status, value)
+    if (f.k_cache) SANDY_FINISH(SANDY_ACT_NONE, true, false, false);                 // the fused q/k/v product: bfloat16, nothing else
+    else if (f.residual) {
+        if (f.out_f32) SANDY_FINISH(SANDY_ACT_NONE, false, true, true);              // x += ...
+        else SANDY_FINISH(SANDY_ACT_NONE, false, true, false);
+    } else if (f.act == SANDY_ACT_GELU_TANH) {
+        if (f.out_f32) SANDY_FINISH(SANDY_ACT_GELU_TANH, false, false, true);
+        else SANDY_FINISH(SANDY_ACT_GELU_TANH, false, false, false);
+    } else if (f.act == SANDY_ACT_GELU_ERF) {
+        if (f.out_f32) SANDY_FINISH(SANDY_ACT_GELU_ERF, false, false, true);
+        else SANDY_FINISH(SANDY_ACT_GELU_ERF, false, false, false);
+    } else {
+        if (f.out_f32) SANDY_FINISH(SANDY_ACT_NONE, false, false, true);
+        else SANDY_FINISH(SANDY_ACT_NONE, false, false, false);
+    }
+#undef SANDY_FINISH
 }
 
 // grid (splits, tiles), clusters of (splits, 1, 1): blockIdx.x is the block's rank in its cluster.
@@ -179,6 +245,7 @@ gemm_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int n = n0 + col;
     const int e = threadIdx.x - 64;               // 0..127 among the write-back threads
     float bias = 0.0f;
+    const Finish fin = make_finish(ep);
     float* part = reinterpret_cast<float*>(smem);     // the ring is idle once the accumulator is complete
     if (warp >= 2) {
         if (ep.bias && n < N) bias = __bfloat162float(ep.bias[n]);     // a weight-like input: before the wait
@@ -201,9 +268,9 @@ gemm_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 for (int j = 0; j < 32; j++) r[j] = 0u;              // a block without k-steps adds zeros
             }
             if (splits == 1) {
-#pragma unroll
-                for (int j = 0; j < 32; j++)
-                    if (c * 32 + j < M) finish(__uint_as_float(r[j]), c * 32 + j, n, bias, ep, N, kv_page, kv_slot, status);
+                const int count = min(32, M - c * 32);
+                finish_dispatch<32>(c * 32, 1, count, n, bias, fin, N, kv_page, kv_slot, status,
+                                    [&](int i) { return __uint_as_float(r[i]); });
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; j++) part[(c * 32 + j) * BM + col] = __uint_as_float(r[j]);
@@ -214,16 +281,17 @@ gemm_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         cluster_sync_all();                       // every block's accumulator is in its shared memory
         if (warp >= 2) {
             const uint32_t part_addr = smem_u32(part);
-            for (int m = split; m < M; m += splits) {
-                const uint32_t at = part_addr + (uint32_t)((m * BM + col) * 4);
+            const int count = M > split ? (M - split + splits - 1) / splits : 0;      // tokens split, split + splits, ...
+            finish_dispatch<0>(split, splits, count, n, bias, fin, N, kv_page, kv_slot, status, [&](int i) {
+                const uint32_t at = part_addr + (uint32_t)((((split + i * splits) * BM) + col) * 4);
                 float v[MAX_SPLITS];
 #pragma unroll
                 for (int s = 0; s < MAX_SPLITS; s++) v[s] = s < splits ? ld_peer(at, (uint32_t)s) : 0.0f;
                 float sum = v[0];
 #pragma unroll
                 for (int s = 1; s < MAX_SPLITS; s++) sum += v[s];                  // the blocks in order
-                finish(sum, m, n, bias, ep, N, kv_page, kv_slot, status);
-            }
+                return sum;
+            });
         }
         cluster_sync_all();                       // nobody leaves while a peer may still read its memory
     }
@@ -260,15 +328,23 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const EpilogueArgs& ep,
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = Layout<STAGES>::TOTAL;
     cfg.stream = stream;
+    // (a product that is not split is launched as an ordinary grid, not as clusters of one block)
     cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    int n_attr = 0;
+    if (splits > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = splits;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        n_attr++;
+    }
+    if (sandy_pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = sandy_pdl_enabled() ? 2 : 1;
+    cfg.numAttrs = n_attr;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_small_kernel<STAGES>, mw, ma, ep, M, N, K, steps, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

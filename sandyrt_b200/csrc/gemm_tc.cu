@@ -420,7 +420,7 @@ SANDY_API int sandy_gemm_tc(const void* a, const void* w, const void* bias, cons
         if (!v_cache || !block_table || !token_seq || !positions || head_dim <= 0 || head_dim % 16 != 0 ||
             kv_cols % head_dim != 0 || q_cols % 8 != 0 || q_cols + 2 * kv_cols != N || page_size <= 0 ||
             (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15) ||
-            page_stride % 8 != 0)
+            page_stride % 8 != 0 || act != SANDY_ACT_NONE)          // (the write-back has no form with both)
             return SANDY_ERR_ARGUMENT;
     }
     EpilogueArgs ep{(const bf16*)bias, residual, out, ldr, ldc, act, out_dtype == SANDY_F32 ? 1 : 0, kv, 0};

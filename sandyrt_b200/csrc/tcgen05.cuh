@@ -163,6 +163,17 @@ __device__ __forceinline__ void kv_row_target(const KVWrite& kv, int row, int M,
     if (pos >= 0 && b < kv.max_blocks) page = kv.block_table[(size_t)kv.token_seq[row] * kv.max_blocks + b];
 }
 
+// The activation as a template argument.  Chosen per element at run time (apply_act_fast with the kernel's
+// `act`), the compiler computed every activation for every element and picked one; the same went for the cache
+// address of the key/value write with its divisions.  So what a product has of these is decided once per
+// warp, outside the element loops (write_back_warp), and the loops are instantiated for each case.
+template <int ACT>
+__device__ __forceinline__ float act_of(float v) {
+    if (ACT == SANDY_ACT_GELU_TANH) return gelu_tanh_fast(v);
+    if (ACT == SANDY_ACT_GELU_ERF) return gelu_erf(v);
+    return v;
+}
+
 // The residual values of 32 consecutive columns of one row, asked for before the accumulator is
 // read so that the trip to memory overlaps the tensor-memory load.  False (nothing loaded) if
 // there is no residual or it cannot be fetched as eight aligned float4; store_chunk then reads
@@ -179,13 +190,14 @@ __device__ __forceinline__ bool load_residual(float4 (&res)[8], int row, int col
 // Write-back of 32 consecutive columns of one row: bias, activation, residual, rounding, store.
 // kv_page, kv_slot: from kv_row_target, used when the chunk holds key or value columns.
 // my_bias: the bias of column col0 + lane (load_bias), handed round by shuffles.
+template <int ACT, bool KV>
 __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int row, int col0, const EpilogueArgs& ep, int M,
                                             int N, const float4 (&res)[8], bool have_res, int kv_page, int kv_slot,
                                             int* status, float my_bias) {
     float v[32];
 #pragma unroll
-    for (int j = 0; j < 32; j++) v[j] = apply_act_fast(__uint_as_float(r[j]) + __shfl_sync(0xffffffffu, my_bias, j), ep.act);
-    if (ep.kv.k_cache && row < M && col0 + 32 > ep.kv.q_cols) {
+    for (int j = 0; j < 32; j++) v[j] = act_of<ACT>(__uint_as_float(r[j]) + __shfl_sync(0xffffffffu, my_bias, j));
+    if (KV && row < M && col0 + 32 > ep.kv.q_cols) {
         // key / value columns also go straight into the request's page, eight at a time (a head's
         // size is a multiple of 16, so eight consecutive columns never straddle two heads)
         if (kv_page < 0 || kv_page >= ep.kv.num_pages) {
@@ -296,6 +308,7 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 // activation, rounding, into the warp's tile; `h` is the chunk's place in the tile (bfloat16: 0 or 1,
 // float: 0).  Key and value columns also go to the cache.
 // my_bias: the bias of column col0 + lane (load_bias).
+template <int ACT, bool KV>
 __device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], uint8_t* tile, int h, int row, int col0,
                                             const EpilogueArgs& ep, int M, int N, int kv_page, int kv_slot, int* status,
                                             float my_bias) {
@@ -308,11 +321,11 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], uint8_t* ti
             float v[4];
 #pragma unroll
             for (int e = 0; e < 4; e++)
-                v[e] = apply_act_fast(__uint_as_float(r[4 * j + e]) + __shfl_sync(0xffffffffu, my_bias, 4 * j + e), ep.act);
+                v[e] = act_of<ACT>(__uint_as_float(r[4 * j + e]) + __shfl_sync(0xffffffffu, my_bias, 4 * j + e));
             *reinterpret_cast<float4*>(my_row + ((j ^ twist) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
         }
     } else {
-        const bool to_cache = ep.kv.k_cache && row < M && col0 + 32 > ep.kv.q_cols;
+        const bool to_cache = KV && row < M && col0 + 32 > ep.kv.q_cols;
         const bool page_ok = kv_page >= 0 && kv_page < ep.kv.num_pages;
         if (to_cache && !page_ok && status) atomicOr(status, 8);
 #pragma unroll
@@ -320,7 +333,7 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], uint8_t* ti
             float v[8];
 #pragma unroll
             for (int e = 0; e < 8; e++)
-                v[e] = apply_act_fast(__uint_as_float(r[8 * q + e]) + __shfl_sync(0xffffffffu, my_bias, 8 * q + e), ep.act);
+                v[e] = act_of<ACT>(__uint_as_float(r[8 * q + e]) + __shfl_sync(0xffffffffu, my_bias, 8 * q + e));
             const __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
             const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
             uint4 pk;
@@ -332,7 +345,7 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], uint8_t* ti
             // eight columns from a multiple of eight never straddle the query / key / value ranges or two
             // heads (the host checks q_cols % 8 == 0 and head_dim % 16 == 0)
             const int col = col0 + 8 * q;
-            if (to_cache && page_ok && col >= ep.kv.q_cols && col + 8 <= N) {
+            if (KV && to_cache && page_ok && col >= ep.kv.q_cols && col + 8 <= N) {
                 const int c = col - ep.kv.q_cols;
                 const bool is_v = c >= ep.kv.kv_cols;
                 const int c2 = is_v ? c - ep.kv.kv_cols : c;
@@ -386,8 +399,8 @@ __device__ __forceinline__ float bias_of(const float (&b)[NCHUNKS], int c) {
 // filled while the copy engine still reads the other.  Chunks leave tensor memory two at a time (one
 // wait for both loads).  after_loads() runs once the last chunk has left tensor memory (the persistent
 // kernels hand the accumulator back there).
-template <int NCHUNKS, int NTILES, typename AfterLoads>
-__device__ __forceinline__ void write_back_warp(uint32_t taddr, uint8_t* tiles, int row0, int col_first, const EpilogueArgs& ep,
+template <int NCHUNKS, int NTILES, int ACT, bool KV, typename AfterLoads>
+__device__ __forceinline__ void write_back_warp_as(uint32_t taddr, uint8_t* tiles, int row0, int col_first, const EpilogueArgs& ep,
                                                 const CUtensorMap* map_out, int M, int N, int kv_page, int kv_slot, int* status,
                                                 const float (&bias)[NCHUNKS], AfterLoads after_loads) {
     static_assert(NTILES == 1 || NTILES == 2, "one or two staging tiles");
@@ -402,7 +415,7 @@ __device__ __forceinline__ void write_back_warp(uint32_t taddr, uint8_t* tiles, 
             tmem_ld_32x32(taddr + (uint32_t)(c * 32), r);
             tmem_wait_ld();
             if (c == NCHUNKS - 1) after_loads();
-            store_chunk(r, row, col_first + c * 32, ep, M, N, res, have_res, kv_page, kv_slot, status, bias_of(bias, c));
+            store_chunk<ACT, KV>(r, row, col_first + c * 32, ep, M, N, res, have_res, kv_page, kv_slot, status, bias_of(bias, c));
         }
         return;
     }
@@ -437,30 +450,50 @@ __device__ __forceinline__ void write_back_warp(uint32_t taddr, uint8_t* tiles, 
             // a float tile is one chunk wide
             tile_free();
             uint8_t* tile = tiles + (stores % NTILES) * EPI_WARP_BYTES;
-            stage_chunk(ra, tile, 0, row, col0, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0));
+            stage_chunk<ACT, KV>(ra, tile, 0, row, col0, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0));
             send(tile, col0);
             if (two) {
                 tile_free();
                 tile = tiles + (stores % NTILES) * EPI_WARP_BYTES;
-                stage_chunk(rb, tile, 0, row, col0 + 32, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0 + 1));
+                stage_chunk<ACT, KV>(rb, tile, 0, row, col0 + 32, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0 + 1));
                 send(tile, col0 + 32);
             }
         } else if (two) {
             // a bfloat16 tile is two chunks wide
             tile_free();
             uint8_t* tile = tiles + (stores % NTILES) * EPI_WARP_BYTES;
-            stage_chunk(ra, tile, 0, row, col0, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0));
-            stage_chunk(rb, tile, 1, row, col0 + 32, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0 + 1));
+            stage_chunk<ACT, KV>(ra, tile, 0, row, col0, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0));
+            stage_chunk<ACT, KV>(rb, tile, 1, row, col0 + 32, ep, M, N, kv_page, kv_slot, status, bias_of(bias, c0 + 1));
             send(tile, col0);
         } else {
             // a last bfloat16 chunk that fills only half of a tile's rows: the store would write the other
             // half too, so this chunk goes out of the registers
             float4 res[8];
-            store_chunk(ra, row, col0, ep, M, N, res, false, kv_page, kv_slot, status, bias_of(bias, c0));
+            store_chunk<ACT, KV>(ra, row, col0, ep, M, N, res, false, kv_page, kv_slot, status, bias_of(bias, c0));
         }
     }
     if (lane == 0) bulk_wait_read();       // the staging memory may be reused (or die) after this
     __syncwarp();
+}
+
+// The write-back of a warp, instantiated for what the product has: the key/value write (never with an
+// activation: the host refuses that), one of the activations, or neither.
+template <int NCHUNKS, int NTILES, typename AfterLoads>
+__device__ __forceinline__ void write_back_warp(uint32_t taddr, uint8_t* tiles, int row0, int col_first, const EpilogueArgs& ep,
+                                                const CUtensorMap* map_out, int M, int N, int kv_page, int kv_slot, int* status,
+                                                const float (&bias)[NCHUNKS], AfterLoads after_loads) {
+    if (ep.kv.k_cache)
+        write_back_warp_as<NCHUNKS, NTILES, SANDY_ACT_NONE, true>(taddr, tiles, row0, col_first, ep, map_out, M, N, kv_page, kv_slot,
+                                                                  status, bias, after_loads);
+    else if (ep.act == SANDY_ACT_GELU_TANH)
+        write_back_warp_as<NCHUNKS, NTILES, SANDY_ACT_GELU_TANH, false>(taddr, tiles, row0, col_first, ep, map_out, M, N, kv_page,
+                                                                        kv_slot, status, bias, after_loads);
+    else if (ep.act == SANDY_ACT_GELU_ERF)
+        write_back_warp_as<NCHUNKS, NTILES, SANDY_ACT_GELU_ERF, false>(taddr, tiles, row0, col_first, ep, map_out, M, N, kv_page,
+                                                                       kv_slot, status, bias, after_loads);
+    else
+        write_back_warp_as<NCHUNKS, NTILES, SANDY_ACT_NONE, false>(taddr, tiles, row0, col_first, ep, map_out, M, N, kv_page, kv_slot,
+                                                                   status, bias, after_loads);
 }
 
 // ---- host side: tensor maps ------------------------------------------------------------
