@@ -482,6 +482,24 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
         const bool fits = stage * 4 <= 160 * 1024;           // the ring holds at least four stages
         static const int bulk_mode = env_int("SANDYRT_DECODE_BULK", -1);      // 0 / 1 force one kernel, for comparisons
         const bool bulk = fits && (bulk_mode < 0 ? T * n_heads >= kBulkMinPairs : bulk_mode == 1);
+        // bfloat16 heads of 64: the products on mma.sync (attention_decode_mma.cu).  Timed alone on caches from
+        // HBM, 12 heads, 400 keys (us; register / bulk / mma.sync kernel): 1 token 4.5 / 5.2 / 3.4; 8 tokens 6.0 /
+        // 7.5 / 5.1; 24 tokens 15.9 / 17.4 / 11.7; 48 tokens 25.9 / 23.2 / 16.0; 64 tokens 45 / 17.5 / 19.9; and
+        // 8 tokens of 1,000 keys 12.9 / 12.5 / 7.8.  So it takes every launch but those with so many pairs that
+        // a pair is one block (one split), where the bulk kernel's deeper ring of pages keeps its small lead.
+        static const int mma_mode = env_int("SANDYRT_DECODE_MMA", 1);          // 0 keeps the two kernels below, for comparisons
+        if (mma_mode != 0 && q.dtype == DType::BF16 && d == 64 && !(bulk && splits == 1)) {
+            static auto max_keys_fn = SANDY_KERNEL(attention_decode_mma, sandy_decode_attention_mma_max_keys);
+            if (max_kv <= max_keys_fn(splits, c.page_size)) {
+                static auto fn = SANDY_KERNEL(attention_decode_mma, sandy_decode_attention_mma);
+                OpTimer timer(l, "attention, decode (mma.sync)", attn_bytes, attn_flops);
+                check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data,
+                         (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, splits, c.num_pages, max_kv, l.kernel_status,
+                         l.stream),
+                      "decode_attention_mma" + shape);
+                return;
+            }
+        }
         if (bulk) {
             static auto fn = SANDY_KERNEL(attention_decode_bulk, sandy_decode_attention_bulk);
             OpTimer timer(l, "attention, decode (bulk copies)", attn_bytes, attn_flops);

@@ -43,6 +43,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention": [],
     "attention_decode": [],
     "attention_decode_bulk": [],
+    "attention_decode_mma": [],
     "attention_prefill": [],
     "attention_prefill_tc": [],
     "sampling": [],

@@ -228,12 +228,13 @@ CLUSTER_MAX_SPLITS = 8
 
 def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int,
                      scale: float, window: int = 0, num_splits: int = 1, scratch=None, cluster: bool = False,
-                     bulk: bool = False) -> None:
+                     bulk: bool = False, mma: bool = False) -> None:
     """Split-KV attention of single tokens (head sizes 16/32/64/128, 256 in bfloat16).  With
     `cluster` (2..8 splits) the splits merge through distributed shared memory inside one
     kernel; otherwise they go through `scratch` and a merge kernel.  `bulk` (at most 8 splits)
     runs the variant that streams whole pages into shared memory with bulk copies, which is
-    the faster one when there are hundreds of (token, head) pairs."""
+    the faster one when there are hundreds of (token, head) pairs.  `mma` (bfloat16, heads of 64, at
+    most 8 splits) runs the variant whose products are mma.sync instructions."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, scratch)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
@@ -245,6 +246,20 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
             or q.dtype != k_cache.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
     _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
+    if mma:
+        if q.dtype != torch.bfloat16 or d != 64:
+            raise UnsupportedShape("decode_attention: the mma.sync kernel takes bfloat16 heads of 64")
+        if num_splits > CLUSTER_MAX_SPLITS:
+            raise UnsupportedShape(f"decode_attention: a cluster holds at most {CLUSTER_MAX_SPLITS} splits")
+        lib = load_library("attention_decode_mma")
+        code = lib.sandy_decode_attention_mma(
+            _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride),
+            _p(block_table), ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
+            ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d),
+            ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_splits),
+            ctypes.c_int(num_pages), ctypes.c_int(block_table.shape[1] * ps), _p(kernel_status(q.device)), _stream())
+        _check(code, f"decode_attention_mma(H={n_heads},Hkv={hkv},page={ps},splits={num_splits})")
+        return
     if bulk:
         if num_splits > CLUSTER_MAX_SPLITS:
             raise UnsupportedShape(f"decode_attention: a cluster holds at most {CLUSTER_MAX_SPLITS} splits")

@@ -76,6 +76,13 @@ int sandy_decode_attention(const void* q, int ld_q, const void* k_cache, const v
                            int page_size, float scale, int window, int num_splits, int num_pages, int dtype, int* status,
                            cudaStream_t stream);
 
+/* attention_decode_mma.cu */
+int sandy_decode_attention_mma_max_keys(int num_splits, int page_size);
+int sandy_decode_attention_mma(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                               const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
+                               int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                               int window, int num_splits, int num_pages, int max_keys, int* status, cudaStream_t stream);
+
 /* attention_decode_bulk.cu */
 int sandy_decode_attention_bulk(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                                 const int* block_table, int max_blocks, const int* token_seq, const int* positions,

@@ -349,7 +349,45 @@ def test_decode_attention_bulk(dtype, H, Hkv, D, page_size, window, splits):
     assert (out.double().cpu() - want).abs().max().item() < ATT_TOL[dtype]
 
 
-@pytest.mark.parametrize("kernel", ["general", "decode", "bulk"])
+@pytest.mark.parametrize("H,Hkv,page_size,window", [(12, 12, 16, 0), (6, 2, 8, 0), (5, 5, 16, 100), (3, 1, 4, 9),
+                                                   (2, 2, 64, 0), (4, 4, 16, 333)])
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
+def test_decode_attention_mma(H, Hkv, page_size, window, splits):
+    """The variant whose products are mma.sync instructions (bfloat16, heads of 64): contexts of 1 to
+    700 keys (tiles of 64 keys: more tiles than stages, last tiles partly filled, ranges that begin and
+    end inside a tile), grouped heads, windows, every split count; and slots of the cache that hold no
+    key of the request are poisoned, so a weight of zero that met one would show."""
+    from sandyrt_b200.csrc import ops
+
+    D, dtype = 64, torch.bfloat16
+    seqs = [(699, 1), (0, 1), (63, 1), (64, 1), (300, 1), (15, 1), (128, 1), (65, 1), (511, 1)]
+    case = _paged_case(dtype, H, Hkv, D, page_size, seqs, seed=7 + splits)
+    # poison every slot behind a request's last position and every page no request holds
+    kc, vc, table = case["kc"], case["vc"], case["table"].cpu()
+    used = torch.zeros(kc.shape[0], page_size, dtype=torch.bool)
+    for s_i, (before, n) in enumerate(seqs):
+        for pos in range(before + n):
+            used[int(table[s_i, pos // page_size]), pos % page_size] = True
+    mask = (~used).to(DEV)[:, None, :, None].expand(-1, Hkv, -1, D)
+    kc[mask] = float("nan")
+    vc[mask] = float("inf")
+    out = torch.full_like(case["q"], float("nan"))
+    scale = 1.0 / math.sqrt(D)
+    run = lambda: ops.decode_attention(case["q"], kc, vc, case["table"], case["tok_seq"], case["tok_pos"], out,
+                                       n_heads=H, scale=scale, window=window, num_splits=splits, mma=True)
+    if case["table"].shape[1] * page_size > (160 - 2) * page_size * splits:
+        # a block keeps the page numbers of its range in shared memory: more pages than it holds are refused
+        with pytest.raises(ops.UnsupportedShape):
+            run()
+        return
+    run()
+    ops.check_kernel_status(DEV)
+    want = _attention_want(case, H, Hkv, D, scale, window)
+    assert bool(torch.isfinite(out.float()).all())
+    assert (out.double().cpu() - want).abs().max().item() < ATT_TOL[dtype]
+
+
+@pytest.mark.parametrize("kernel", ["general", "decode", "bulk", "mma"])
 def test_one_far_key_among_hundreds(kernel):
     """Scale one query/key pair so that a single score dominates: a kernel that dropped or
     misplaced that key (a page's edge, a split's edge) returns a visibly different output."""
@@ -361,8 +399,15 @@ def test_one_far_key_among_hundreds(kernel):
     for far, ps in ((0, 16), (15, 16), (16, 16), (255, 16), (256, 16), (399, 16), (511, 16), (640, 16),
                     (0, 4), (255, 4), (257, 4), (640, 4)):
         seqs = [(641, 1), (5, 1)]
-        case = _paged_case(torch.float32, H, Hkv, D, ps, seqs, seed=far, spike=(0, far))
+        case = _paged_case(torch.bfloat16 if kernel == "mma" else torch.float32, H, Hkv, D, ps, seqs, seed=far, spike=(0, far))
         out = torch.full_like(case["q"], float("nan"))
+        if kernel == "mma":
+            ops.decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"],
+                                 out, n_heads=H, scale=0.125, num_splits=7, mma=True)
+            got = out[0].view(H, D).float().cpu()
+            v_far = case["dense_v"][0][far].float()
+            assert (got - v_far).abs().max().item() < 3e-2, f"far key {far}: output is not that key's value"
+            continue
         if kernel == "general":
             ops.paged_attention(case["q"], case["kc"], case["vc"], case["table"], case["tok_seq"], case["tok_pos"],
                                 out, n_heads=H, scale=0.125)
