@@ -298,6 +298,10 @@ Json call_global(const std::string& m, const Json& a) {
         ops::leave_out(families);
         return Json();
     }
+    if (m == "force_tile") {                          // {"N", "K", "tile"}: the tcgen05 variant of one weight shape; 0 restores
+        ops::force_tile(a.at("N").as_int(), a.at("K").as_int(), (int)a.at("tile").as_int());
+        return Json();
+    }
     if (m == "profile_kernels") {                     // {"enable": bool} -> what was gathered since it was switched on
         Json out = Json::array();
         for (const ops::ProfileRow& r : ops::profile_report()) {

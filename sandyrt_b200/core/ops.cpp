@@ -198,8 +198,8 @@ bool tensor_core_gemm_supported(int64_t K, int64_t N) {
 // steps of 128) with at least 256 rows times each variant on a scratch output and remembers the
 // winner.  All variants add the k-steps of an output element in the same order, so the choice never
 // changes a result.  Not done while a CUDA graph is being captured (the kernel's own default stands
-// then).  Tile codes: n > 0 one tile of 128 x n per CTA, n < 0 the persistent kernel with tiles of
-// 128 x |n|, kPairTile + n two CTAs on a 256 x n tile.
+// then).  Tile codes: n < 0 one tile of 128 x |n| per CTA, n > 0 the persistent kernel with tiles of
+// 128 x n, kPairTile + n two CTAs on a 256 x n tile.
 constexpr int kPairTile = 2000;
 constexpr int kGemmTuneMinRows = 256;
 constexpr int kTuneLaunches = 8;
@@ -208,6 +208,7 @@ const int kGemmVariants[] = {-64, -128, -256, 64, 128, 256, kPairTile + 128, kPa
 namespace {
 using TileKey = std::tuple<int64_t, int64_t, int64_t, int, bool, int>;
 std::map<TileKey, int> g_tiles;
+std::map<std::pair<int64_t, int64_t>, int> g_forced_tiles;      // (N, K) -> variant, for comparisons (force_tile)
 
 struct TcArgs {
     const Tensor* a; const Tensor* w; const Tensor* bias; Act act; int64_t M, N, K;
@@ -257,6 +258,10 @@ void gemm_tc(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bi
                   tensor_bytes(&a) + tensor_bytes(&w) + tensor_bytes(&out) + 2 * tensor_bytes(residual), 2.0 * M * N * K);
     const TcArgs g{&a, &w, bias, act, M, N, K};
     const TileKey key{(M + 127) / 128, N, K, (int)act, residual != nullptr, (int)out.dtype};
+    if (tile_n == 0 && !g_forced_tiles.empty() && M >= kGemmTuneMinRows) {
+        auto forced = g_forced_tiles.find({N, K});
+        if (forced != g_forced_tiles.end()) tile_n = forced->second;
+    }
     if (tile_n == 0) {
         auto hit = g_tiles.find(key);
         if (hit != g_tiles.end()) tile_n = hit->second;
@@ -300,6 +305,14 @@ void gemm_tc(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bi
     }
     launch_tc(l, g, tile_n, out, residual, kv);
     if (kv) kv->written = true;
+}
+
+// The variant that products of W [N, K] with at least 256 rows take from now on, whatever the tuner
+// found (0: the tuner's choice again).  For comparing variants inside a whole step; steps already
+// recorded as graphs keep what they were recorded with.
+void force_tile(int64_t N, int64_t K, int tile) {
+    if (tile == 0) g_forced_tiles.erase({N, K});
+    else g_forced_tiles[{N, K}] = tile;
 }
 
 // ---- the weight-streaming product ---------------------------------------------------------------------

@@ -42,6 +42,7 @@ void profile_enable(bool on);
 // Families of launches that are skipped from now on ("layernorm", "attention", "kv_append", "product",
 // "product <N>x<K>"): for timing what a family costs inside a step; results are garbage meanwhile.
 void leave_out(const std::vector<std::string>& families);
+void force_tile(int64_t N, int64_t K, int tile);      // tcgen05 variant for products of W [N, K]; 0: the tuner's
 std::vector<ProfileRow> profile_report();              // also clears what was gathered
 
 int sm_count();                                        // streaming multiprocessors of the current device

@@ -1,6 +1,7 @@
 """Each part alone against the plain implementation's function for it, and a toy model made
 of parts the framework has never seen: a mixer with a state of its own, different mixers in
-different layers, a layer that runs twice and a layer that reads another layer's cache."""
+different layers, a layer that runs twice and a layer that reads another layer's cache; a
+position encoding that turns queries and keys; a feed-forward with routing and another norm."""
 import dataclasses
 import json
 import math
@@ -440,4 +441,179 @@ def test_position_encoding_that_rotates_queries_and_keys(tmp_path, dtype, atol, 
             pos += n
         eng.release("r")
         np.testing.assert_allclose(np.concatenate(rows), want, atol=atol, rtol=rtol, err_msg=f"cuts {cuts}")
+    eng.check_status()
+
+
+# ---- a feed-forward with routing, and a norm of another kind -----------------------------------
+def _register_routed():
+    """Registers, from outside the framework: a feed-forward that sends every token to the best
+    `top` of its experts (router logits and their softmax in float32; an expert is two small
+    matrices with a squared ReLU between), a norm without a mean (root mean square, one gain), and
+    an architecture whose layers differ: the first has the routed feed-forward, the second the
+    library's dense one, and both use the toy norm in front of the feed-forward only."""
+    from sandyrt_b200.config.base import ModelConfig
+    from sandyrt_b200.models.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
+    from sandyrt_b200.parts.base import FeedForward, Norm
+    from sandyrt_b200.registry import register_architecture, register_part
+    from sandyrt_b200.weights.loader import TensorRequest
+
+    class RoutedFF(FeedForward):
+        graph_safe = False        # the number of tokens an expert gets is read on the host
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            p = self.params
+            self.width, self.inner, self.n, self.top = int(p["width"]), int(p["inner"]), int(p["experts"]), int(p["top"])
+
+        def requests(self):
+            E, I, n = self.width, self.inner, self.n
+            return {"router": TensorRequest((n, E)), "up": TensorRequest((n, I, E)), "down": TensorRequest((n, E, I))}
+
+        def bind(self, tensors, device, dtype):
+            self.router = tensors["router"].to(device=device, dtype=torch.float32)       # routing stays in float32
+            self.up = tensors["up"].to(device=device, dtype=dtype)
+            self.down = tensors["down"].to(device=device, dtype=dtype)
+
+        def forward(self, ctx, h, x):
+            logits = h.float() @ self.router.T
+            best, which = torch.topk(logits, self.top, dim=-1)
+            gate = torch.softmax(best, dim=-1)                                            # over the chosen experts only
+            for e in range(self.n):
+                tok, k = torch.nonzero(which == e, as_tuple=True)
+                if tok.numel() == 0:
+                    continue
+                a = torch.relu(h[tok] @ self.up[e].T) ** 2
+                x.index_add_(0, tok, (a.to(h.dtype) @ self.down[e].T).float() * gate[tok, k][:, None])
+
+    class RmsNorm(Norm):
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.width, self.eps = int(self.params["width"]), float(self.params["eps"])
+
+        def requests(self):
+            return {"gain": TensorRequest((self.width,), init="gamma")}
+
+        def bind(self, tensors, device, dtype):
+            self.gain = tensors["gain"].to(device=device, dtype=torch.float32)
+
+        def forward(self, ctx, x, out, rows=None):
+            src = x if rows is None else x[rows.long()]
+            y = src * torch.rsqrt((src * src).mean(dim=-1, keepdim=True) + self.eps) * self.gain
+            out.copy_(y.to(out.dtype))
+
+    @dataclasses.dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        architecture = "ToyRoutedModel"
+        width: int = 0
+        vocab_size: int = 0
+        experts: int = 0
+        top: int = 1
+        eps: float = 1e-6
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(**{k: raw[k] for k in ("width", "vocab_size", "experts", "top", "eps")})
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "width": self.width, "vocab_size": self.vocab_size,
+                    "experts": self.experts, "top": self.top, "eps": self.eps}
+
+        def validate(self):
+            assert self.width % 16 == 0 and 1 <= self.top <= self.experts
+
+    def describe(cfg):
+        E = cfg.width
+        ln = lambda n: PartSpec("layernorm", {"width": E, "eps": 1e-5}, {"weight": n + ".g", "bias": n + ".b"})
+        rms = lambda n: PartSpec("toy_rms", {"width": E, "eps": cfg.eps}, {"gain": n + ".gain"})
+        attn = lambda p: PartSpec("causal_attention", {"width": E, "n_heads": 3, "n_kv_heads": 3, "head_dim": E // 3,
+                                                       "scale": 1 / math.sqrt(E // 3), "weight_layout": "out_in"},
+                                  {"qkv.weight": p + "qkv.w", "qkv.bias": p + "qkv.b", "out.weight": p + "o.w",
+                                   "out.bias": p + "o.b"})
+        layers = [
+            LayerSpec("pre_norm", attn("l0."),
+                      PartSpec("toy_routed", {"width": E, "inner": E + 16, "experts": cfg.experts, "top": cfg.top},
+                               {"router": "l0.router", "up": "l0.up", "down": "l0.down"}),
+                      {"mixer": ln("l0.n1"), "feed_forward": rms("l0.n2")}),
+            LayerSpec("pre_norm", attn("l1."),
+                      PartSpec("dense_mlp", {"width": E, "inner": 2 * E, "activation": "gelu_new", "weight_layout": "out_in"},
+                               {"up.weight": "l1.up.w", "up.bias": "l1.up.b", "down.weight": "l1.dn.w", "down.bias": "l1.dn.b"}),
+                      {"mixer": ln("l1.n1"), "feed_forward": rms("l1.n2")}),
+        ]
+        return ModelSpec(architecture=cfg.architecture, width=E, vocab_size=cfg.vocab_size, max_positions=None,
+                         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "width": E}, {"weight": "emb"}),
+                         position=PartSpec("none", {}, {}), layers=layers, schedule=[LayerCall(0, 0), LayerCall(1, 1)],
+                         final_norm=rms("nf"), head=PartSpec("output_head", {"vocab_size": cfg.vocab_size, "width": E,
+                                                                             "tied": True}, {}))
+
+    register_part("feed_forward", "toy_routed", RoutedFF)
+    register_part("norm", "toy_rms", RmsNorm)
+    register_architecture("ToyRoutedModel", RoutedConfig, describe)
+    return RoutedConfig
+
+
+def _routed_plain_logits(w, ids, E, top, eps):
+    """The routed toy model, whole sequence, token by token where the routing is."""
+    T, D = len(ids), E // 3
+    x = plain.embedding(ids, w["emb"])
+    ln = lambda x, n: plain.layer_norm(x, w[n + ".g"], w[n + ".b"], 1e-5)
+    rms = lambda x, n: x / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps) * w[n + ".gain"]
+    lin = lambda h, p: plain.linear_in_out(h, w[p + "w"].T, w[p + "b"])
+    split = lambda t: t.reshape(T, 3, D).transpose(1, 0, 2)
+
+    def attn(x, p):
+        qkv = lin(ln(x, p + "n1"), p + "qkv.")
+        o = plain.causal_attention(split(qkv[:, :E]), split(qkv[:, E:2 * E]), split(qkv[:, 2 * E:]), 1 / math.sqrt(D))
+        return x + lin(o.transpose(1, 0, 2).reshape(T, E), p + "o.")
+
+    x = attn(x, "l0.")
+    h = rms(x, "l0.n2")
+    chosen = []
+    for t in range(T):
+        logits = w["l0.router"] @ h[t]
+        order = np.argsort(-logits)[:top]
+        g = np.exp(logits[order] - logits[order].max()); g /= g.sum()
+        chosen.append(tuple(int(e) for e in order))
+        for e, ge in zip(order, g):
+            x[t] += ge * (w["l0.down"][e] @ (np.maximum(w["l0.up"][e] @ h[t], 0) ** 2))
+    x = attn(x, "l1.")
+    x = x + lin(plain.gelu_new(lin(rms(x, "l1.n2"), "l1.up.")), "l1.dn.")
+    return rms(x, "nf") @ w["emb"].T, chosen
+
+
+@pytest.mark.parametrize("top", [1, 2])
+def test_feed_forward_with_routing_and_a_norm_of_another_kind(tmp_path, top):
+    """A feed-forward that routes and a norm the library does not have, defined here, are
+    registered, built from config.json and stepped in mixed batches; the layers of the model
+    differ in their feed-forward.  Every expert is used, or the test would not see a wrong one."""
+    from sandyrt_b200.engine.step import Engine, StepEntry
+    from sandyrt_b200.models.model import load_model
+    from sandyrt_b200.weights.random_init import write_random_model
+
+    RoutedConfig = _register_routed()
+    cfg = RoutedConfig(width=48, vocab_size=75, experts=3, top=top, eps=1e-4)
+    d = write_random_model(cfg, str(tmp_path / "routed"), seed=8, dtype=torch.float32)
+    model = load_model(d, device=DEV, dtype=torch.float32)
+    assert not model.graph_safe
+    eng = Engine(model, max_tokens=128, page_size=8, max_requests=2)
+    eng.cache.device_caches.poison()
+    w = plain.read_safetensors(os.path.join(d, "model.safetensors"))
+    rng = np.random.default_rng(5)
+    seqs = {name: rng.integers(0, 75, size=n).tolist() for name, n in (("a", 29), ("b", 12), ("c", 21))}
+    want, used = {}, set()
+    for k, ids in seqs.items():
+        want[k], chosen = _routed_plain_logits(w, ids, 48, top, 1e-4)
+        used.update(e for c in chosen for e in c)
+    assert used == {0, 1, 2}
+    plan = [[("a", 11), ("b", 2)], [("a", 1), ("b", 10)], [("a", 1), ("c", 5)], [("c", 16), ("a", 16)]]
+    got, fed = {k: [] for k in seqs}, {k: 0 for k in seqs}
+    for step in plan:
+        out = eng.step([StepEntry(k, seqs[k][fed[k]:fed[k] + n], list(range(n))) for k, n in step]).cpu().numpy()
+        r = 0
+        for k, n in step:
+            got[k].append(out[r:r + n].copy()); r += n; fed[k] += n
+            if fed[k] == len(seqs[k]):
+                eng.release(k)
+        eng.cache.alloc.check()
+    for k in seqs:
+        np.testing.assert_allclose(np.concatenate(got[k]), want[k], atol=5e-5, rtol=1e-4, err_msg=f"sequence {k}")
     eng.check_status()
