@@ -52,7 +52,8 @@ def decode_attention(a) -> int:
     dev = torch.device("cuda:0")
     H, D, PS = a.heads, a.head_dim, a.page_size
     print("tokens context  kernel    splits       us     GB/s")
-    for T, ctx in ((64, 384), (64, 1024), (256, 384), (8, 384), (8, 1024), (1, 1024)):
+    shapes = [tuple(int(v) for v in sh.split("x")) for sh in a.shape]
+    for T, ctx in shapes:
         blocks = -(-ctx // PS)
         pages = T * blocks
         bytes_per_launch = T * ctx * H * D * 2 * 2
@@ -64,13 +65,15 @@ def decode_attention(a) -> int:
         pos = torch.full((T,), ctx - 1, device=dev, dtype=torch.int32)
         out = torch.empty_like(q)
         splits = min(ops.decode_splits(T, H, blocks * PS), ops.CLUSTER_MAX_SPLITS)
-        for bulk in (False, True):
-            def go(l, bulk=bulk):
+        kernels = [("register", dict(bulk=False)), ("bulk", dict(bulk=True))]
+        if D == 64:
+            kernels.append(("mma.sync", dict(mma=True)))
+        for name, which in kernels:
+            def go(l, which=which):
                 ops.decode_attention(q, arena[l, :, 0], arena[l, :, 1], table, seq, pos, out, n_heads=H,
-                                     scale=D ** -0.5, num_splits=splits, cluster=True, bulk=bulk)
+                                     scale=D ** -0.5, num_splits=splits, cluster=True, **which)
             us = _time_graph(go, layers)
-            print(f"{T:6d} {ctx:7d}  {'bulk' if bulk else 'register':8s} {splits:6d} {us:8.2f} {bytes_per_launch / us / 1e3:8.0f}",
-                  flush=True)
+            print(f"{T:6d} {ctx:7d}  {name:8s} {splits:6d} {us:8.2f} {bytes_per_launch / us / 1e3:8.0f}", flush=True)
         ops.check_kernel_status(dev)
         del arena
     return 0
@@ -186,6 +189,8 @@ def main(argv=None) -> int:
     d.add_argument("--heads", type=int, default=12)
     d.add_argument("--head-dim", type=int, default=64)
     d.add_argument("--page-size", type=int, default=16)
+    d.add_argument("--shape", nargs="+", default=["64x384", "64x1024", "256x384", "8x384", "8x1024", "1x1024"],
+                   help="tokens x context")
     d.set_defaults(fn=decode_attention)
     g = sub.add_parser("gemm")
     g.add_argument("--rows", type=int, default=2048)
