@@ -431,8 +431,13 @@ int decode_splits(int n_tokens, int n_heads, int max_kv, int sms) {
     static const int forced = env_int("SANDYRT_DECODE_SPLITS", 0);       // > 0: this many splits, for comparisons
     if (forced > 0) return forced;
     if (sms <= 0) sms = sm_count();
+    // About four blocks an SM in all, to the nearest number of splits.  (Rounded up, as it was for the
+    // register kernel, 12 / 16 / 24 requests of 12 heads got 5 / 4 / 3 splits; whole decode steps with the
+    // mma.sync kernel, GPT-2 small, context ~400, ms by splits 1 / 2 / 3 / 4 / 5: 12 requests .340 / .334 /
+    // .323 / .311 / .342; 16: .361 / .350 / .341 / .361 / .374; 24: .490 / .409 / .455 / .437 / .473; 32:
+    // .509 / .494 / .484 / .512 / .508; 48: .627 / .626 / .664 / .685 / .731; 8: .330 / .323 / .310 / .303 / .306.)
     const int pairs = std::max(1, n_tokens * n_heads);
-    const int want = (4 * sms + pairs - 1) / pairs;
+    const int want = (4 * sms + pairs / 2) / pairs;
     const int cap = std::max(1, max_kv / 64);
     const int n = std::max(1, std::min({want, cap, 32}));
     // The splits of a pair are one thread-block cluster.  Clusters of 6 and 7 blocks pack badly into

@@ -83,6 +83,12 @@ void gemm_tc(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bi
              const Tensor* residual, int tile_n = 0, KVTarget* kv = nullptr);
 // Weight streaming for up to 64 rows (a decode step); optional LayerNorm prologue and key/value write.
 bool skinny_norm_fusable(const FusedNorm& n, int64_t K, DType out_dtype);
+// Up to how many rows running the norm inside the product pays.  Every block of the product norms all
+// rows itself, so that traffic grows with rows x blocks, while the norm as a launch of its own costs a
+// fixed 1.5 us or so behind programmatic dependent launch.  Whole decode steps of GPT-2 small (ms, norm
+// inside / norm apart): 1 request .244 / .250, 2: .255 / .262, 4: .267 / .270, 6: .290 / .285, 7: .297 /
+// .288, 8: .303 / .294, 12: .381 / .341, 16: .409 / .361.
+constexpr int kSkinnyNormPaysRows = 4;
 void gemm_skinny(const Launch& l, const Tensor* a, const FusedNorm* norm, const Tensor& w, const Tensor* bias, Tensor& out,
                  Act act, const Tensor* residual, KVTarget* kv = nullptr);
 constexpr int kSkinnyMaxRows = 64;
