@@ -351,6 +351,149 @@ int launch(const void* a, const NormArgs& norm, const void* w, const void* bias,
     return launch1<MT, FUSE_LN, 16>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
 }
 
+// ---- 17 to 64 rows and many columns: sixteen columns a block ------------------------------------
+// With more than one tile of rows the kernel above is bound by what it reads beside the weight: every
+// block fetches all M rows of the activations (64 rows x 768: 98 KB from L2, against 12 KB of weight
+// for its 8 columns), and with four row tiles it needs 216 registers, one block an SM, so that the 288
+// blocks of a 2,304-column product run in two rounds.  Here a block owns 16 columns (two column
+// tiles of the instruction): every activation fragment feeds four products instead of two, half as
+// many blocks fetch the rows, and with two 16-byte weight pieces a lane in flight per column tile the
+// kernel stays under 128 registers, two blocks an SM.  The sums are formed exactly as above (a warp's
+// k slice in ascending order, then the warps in order), so the two kernels give the same bits.
+// (Copying each warp's k slice of the rows into shared memory first, one trip for all of them, was
+// tried and is slower: decode steps of 17 / 64 requests 0.399 / 0.735 ms against 0.359 / 0.655; the
+// copies stand between the wait for the kernel before and the first product, and 106 KB of shared
+// memory a block leave no room for the next kernel's blocks to start early.)
+constexpr int COLS2 = 16;
+
+template <int MT, typename TC>
+__global__ void __launch_bounds__(WARPS * 32, 2)
+gemm_skinny_wide_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const bf16* __restrict__ bias,
+                        const float* residual, TC* out, int M, int N, int K, int lda, int ldw, int ldr, int ldc, int act,
+                        KVWrite kv) {
+    constexpr int UNROLL = 2;
+    __shared__ float partial[WARPS][MT * 16][COLS2 + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * COLS2;
+    const int chunks = (K + KCHUNK - 1) / KCHUNK;
+    const int per_warp = (chunks + WARPS - 1) / WARPS;
+    const int c_begin = warp * per_warp, c_end = min(chunks, c_begin + per_warp);
+
+    float acc[MT][2][4];
+#pragma unroll
+    for (int i = 0; i < MT; i++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[i][h][j] = 0.0f;
+
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const bf16* wrow[2];
+    bool n_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int n = n0 + 8 * h + g;               // the weight row this lane reads for column tile h
+        n_ok[h] = n < N;
+        wrow[h] = w + (size_t)(n_ok[h] ? n : 0) * ldw;
+    }
+    uint4 wn[2][UNROLL];
+#pragma unroll
+    for (int h = 0; h < 2; h++)
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const int k = (c_begin + u) * KCHUNK + t * 8;
+            wn[h][u] = (n_ok[h] && c_begin + u < c_end && k < K) ? ldg16_stream(wrow[h] + k) : zero;
+        }
+    // thread i writes outputs i, i + 256, ...: always column i % 16 of the block
+    const int my_col = n0 + (int)(threadIdx.x % COLS2);
+    const float my_bias = (bias && my_col < N) ? __bfloat162float(bias[my_col]) : 0.0f;
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    for (int c0 = c_begin; c0 < c_end; c0 += UNROLL) {
+        uint4 wv[2][UNROLL];
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                wv[h][u] = wn[h][u];
+                const int cn = c0 + UNROLL + u;
+                const int k = cn * KCHUNK + t * 8;
+                wn[h][u] = (n_ok[h] && cn < c_end && k < K) ? ldg16_stream(wrow[h] + k) : zero;
+            }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const int k = (c0 + u) * KCHUNK + t * 8;
+            const bool k_ok = c0 + u < c_end && k < K;
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const int r0 = mt * 16 + g, r1 = r0 + 8;
+                const uint4 x0 = (k_ok && r0 < M) ? ldg16(a + (size_t)r0 * lda + k) : zero;
+                const uint4 x1 = (k_ok && r1 < M) ? ldg16(a + (size_t)r1 * lda + k) : zero;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    mma_bf16(acc[mt][h], x0.x, x1.x, x0.y, x1.y, wv[h][u].x, wv[h][u].y);
+                    mma_bf16(acc[mt][h], x0.z, x1.z, x0.w, x1.w, wv[h][u].z, wv[h][u].w);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            partial[warp][mt * 16 + g][8 * h + 2 * t] = acc[mt][h][0];
+            partial[warp][mt * 16 + g][8 * h + 2 * t + 1] = acc[mt][h][1];
+            partial[warp][mt * 16 + g + 8][8 * h + 2 * t] = acc[mt][h][2];
+            partial[warp][mt * 16 + g + 8][8 * h + 2 * t + 1] = acc[mt][h][3];
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < MT * 16 * COLS2; idx += WARPS * 32) {
+        const int m = idx / COLS2, j = idx % COLS2;
+        const int col = n0 + j;
+        if (m >= M || col >= N) continue;
+        float v = partial[0][m][j];
+#pragma unroll
+        for (int wi = 1; wi < WARPS; wi++) v += partial[wi][m][j];
+        v += my_bias;
+        v = apply_act(v, act);
+        if (residual) v += residual[(size_t)m * ldr + col];
+        out[(size_t)m * ldc + col] = from_f32<TC>(v);
+        if (kv.k_cache && col >= kv.q_cols) {
+            // a key or value element: straight into the request's page
+            const int c = col - kv.q_cols;
+            const bool is_v = c >= kv.kv_cols;
+            const int c2 = is_v ? c - kv.kv_cols : c;
+            const int head = c2 / kv.head_dim, d = c2 % kv.head_dim;
+            const int pos = kv.positions[m];
+            const int b = pos / kv.page_size;
+            const int page = (pos >= 0 && b < kv.max_blocks) ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
+            if (page < 0 || page >= kv.num_pages) {
+                if (kv.status) atomicOr(kv.status, 8);
+            } else {
+                const size_t dst = (size_t)page * kv.page_stride +
+                                   ((size_t)head * kv.page_size + (pos % kv.page_size)) * kv.head_dim + d;
+                (is_v ? kv.v_cache : kv.k_cache)[dst] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+constexpr int WIDE_MIN_COLS = 1536;     // from here on half the blocks still fill the GPU
+
+template <int MT>
+int launch_wide(const void* a, const void* w, const void* bias, const float* residual, void* out, int M, int N, int K, int lda,
+                int ldw, int ldr, int ldc, int act, int out_dtype, const KVWrite& kv, cudaStream_t stream) {
+    const unsigned blocks = (unsigned)((N + COLS2 - 1) / COLS2);
+    if (out_dtype == SANDY_F32)
+        return sandy_launch(gemm_skinny_wide_kernel<MT, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const bf16*)a,
+                            (const bf16*)w, (const bf16*)bias, residual, (float*)out, M, N, K, lda, ldw, ldr, ldc, act, kv);
+    return sandy_launch(gemm_skinny_wide_kernel<MT, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const bf16*)a,
+                        (const bf16*)w, (const bf16*)bias, residual, (bf16*)out, M, N, K, lda, ldw, ldr, ldc, act, kv);
+}
+
 // ---- a vocabulary projection: up to 16 rows, very many columns, nothing fused -------------------
 // The kernel above gives every 8 columns a block of eight warps that split K: for 50,257 columns
 // that is 6,283 short-lived blocks, three of them on an SM at a time, each with 12 KB of weights in
@@ -504,6 +647,11 @@ SANDY_API int sandy_gemm_skinny(const void* a, const float* x, int ldx, const vo
     }
     if (fuse) return launch<1, true>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
     if (M <= 16) return launch<1, false>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    if (N >= WIDE_MIN_COLS) {
+        if (M <= 32) return launch_wide<2>(a, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+        if (M <= 48) return launch_wide<3>(a, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+        return launch_wide<4>(a, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
+    }
     if (M <= 32) return launch<2, false>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
     return launch<4, false>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
 }

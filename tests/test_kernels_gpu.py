@@ -615,15 +615,19 @@ def test_gemm_skinny_with_the_norm_inside(M, K, N, eps):
     assert (got.double() - ref).abs().max().item() < 2e-2 * (1 + ref.abs().max().item())
 
 
-def test_gemm_skinny_writes_keys_and_values_into_the_pages():
+@pytest.mark.parametrize("H,Hkv,D,seqs", [
+    (6, 2, 32, [(13, 1), (0, 1), (7, 1), (40, 1), (8, 3)]),
+    # 40 rows and 1,792 columns: the form with sixteen columns a block, three row tiles
+    (12, 8, 64, [(13, 1), (0, 30), (7, 1), (40, 1), (8, 7)]),
+])
+def test_gemm_skinny_writes_keys_and_values_into_the_pages(H, Hkv, D, seqs):
     """The fused q/k/v product puts its key and value columns where kv_append would."""
     from sandyrt_b200.csrc import ops
     from sandyrt_b200.csrc.ops import KVTarget
 
-    H, Hkv, D, ps = 6, 2, 32, 8
+    ps = 8
     q_cols, kv_cols = H * D, Hkv * D
     K = 96
-    seqs = [(13, 1), (0, 1), (7, 1), (40, 1), (8, 3)]
     T = sum(n for _, n in seqs)
     num_pages = 32
     g = torch.Generator().manual_seed(0)
