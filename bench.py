@@ -313,11 +313,12 @@ def workload(name: str, dtype_name: str, layers: int) -> int:
     return 0
 
 
-def attribute(dtype_name: str, layers: int, batch: int) -> int:
+def attribute(dtype_name: str, layers: int, batch: int, prompts: str = "2x1024") -> int:
     """What each family of launches costs INSIDE a step: the step is timed whole and again with the
     family left out (its results are garbage then; only the time is read), and the difference is the
     family's share with all overlap between neighbouring kernels as it is in the real step.  A decode
-    step of `batch` requests at the bench's context and a prompt step of 2 x 1,024 tokens."""
+    step of `batch` requests at the bench's context and a prompt step of `prompts` (requests x tokens;
+    2 x 1,024 unless --attribute-prompts says otherwise)."""
     import numpy as np
 
     from sandyrt_b200 import core
@@ -327,6 +328,7 @@ def attribute(dtype_name: str, layers: int, batch: int) -> int:
     from sandyrt_b200.config.gpt2 import GPT2Config
     cfg = GPT2Config.from_dict(raw)
     E, I, V = cfg.n_embd, cfg.inner_dim, cfg.vocab_size
+    n_prompts, prompt_len = (int(v) for v in prompts.lower().split("x"))
     cases = [("nothing", []), ("layernorm (own launches)", ["layernorm"]), ("attention", ["attention"]),
              (f"q/k/v projection {3 * E}x{E}", [f"product {3 * E}x{E}"]), (f"out-projection {E}x{E}", [f"product {E}x{E}"]),
              (f"up-projection {I}x{E}", [f"product {I}x{E}"]), (f"down-projection {E}x{I}", [f"product {E}x{I}"]),
@@ -340,13 +342,13 @@ def attribute(dtype_name: str, layers: int, batch: int) -> int:
             rng = np.random.default_rng(0)
             llm = LLM(model, cache_tokens=64 * 1024 + 4096, max_live=64, max_step_tokens=4096, prefill_chunk_tokens=2048)
             d_ms, _, ctx, launches = decode_run(llm, batch, 128, 24, 3, rng, V, want_e2e=False)
-            p_ms, _ = prefill_run(llm.engine, V, rng, reps=3)
+            p_ms, _ = prefill_run(llm.engine, V, rng, n_prompts=n_prompts, prompt_len=prompt_len, reps=3)
         finally:
             core.call("global", None, "leave_out", families=[])
         rows.append((name, d_ms * 1e3, launches, p_ms * 1e3))
         del llm, model
     d0, p0 = rows[0][1], rows[0][3]
-    print(f"{dtype_name}, {cfg.n_layer} layers; decode step of {batch} requests at context ~{ctx:.0f}, prompt step of 2 x 1,024 tokens")
+    print(f"{dtype_name}, {cfg.n_layer} layers; decode step of {batch} requests at context ~{ctx:.0f}, prompt step of {n_prompts} x {prompt_len} tokens")
     print(f"  {'left out':32s} {'decode us':>10s} {'saves':>8s} {'per layer':>10s} {'launches':>9s} {'prompt us':>10s} {'saves':>8s} {'per layer':>10s}")
     for name, d, launches, p in rows:
         print(f"  {name:32s} {d:10.1f} {d0 - d:8.1f} {(d0 - d) / cfg.n_layer:10.2f} {launches:9d} {p:10.1f} {p0 - p:8.1f} {(p0 - p) / cfg.n_layer:10.2f}")
@@ -412,6 +414,7 @@ def main() -> int:
     ap.add_argument("--under-profiler", action="store_true",
                     help="skip the check of the device time against the wall clock (a profiler serialises the launches)")
     ap.add_argument("--attribute", action="store_true", help="print what each family of launches costs inside a step instead")
+    ap.add_argument("--attribute-prompts", default="2x1024", help="the prompt step of --attribute: requests x tokens")
     ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -427,7 +430,7 @@ def main() -> int:
     if args.profile_kernels:
         return profile_kernels(args.dtype, args.layers, args.batch)
     if args.attribute:
-        return attribute(args.dtype, args.layers, args.batch)
+        return attribute(args.dtype, args.layers, args.batch, args.attribute_prompts)
     if args.warmup < 3:
         args.warmup = 3
 
