@@ -436,8 +436,14 @@ int decode_splits(int n_tokens, int n_heads, int max_kv, int sms) {
     // mma.sync kernel, GPT-2 small, context ~400, ms by splits 1 / 2 / 3 / 4 / 5: 12 requests .340 / .334 /
     // .323 / .311 / .342; 16: .361 / .350 / .341 / .361 / .374; 24: .490 / .409 / .455 / .437 / .473; 32:
     // .509 / .494 / .484 / .512 / .508; 48: .627 / .626 / .664 / .685 / .731; 8: .330 / .323 / .310 / .303 / .306.)
+    // Long ranges: a block that walks more than some 256 keys alone is the step's longest chain, so a pair is
+    // cut further as long as no more than eight blocks an SM come of it (32 requests at context 965, ms by
+    // splits 1 / 2 / 3 / 4: .741 / .655 / .596 / .633; GPT-2 medium, 32 requests of mixed lengths, tokens a
+    // second with 1 / 2 / 3 splits: 17-19 k / 21-23 k / 21 k).
     const int pairs = std::max(1, n_tokens * n_heads);
-    const int want = (4 * sms + pairs / 2) / pairs;
+    const int by_blocks = (4 * sms + pairs / 2) / pairs;
+    const int by_length = std::min((max_kv + 255) / 256, (8 * sms) / pairs);
+    const int want = std::max(by_blocks, by_length);
     const int cap = std::max(1, max_kv / 64);
     const int n = std::max(1, std::min({want, cap, 32}));
     // The splits of a pair are one thread-block cluster.  Clusters of 6 and 7 blocks pack badly into
