@@ -313,7 +313,7 @@ def workload(name: str, dtype_name: str, layers: int) -> int:
     return 0
 
 
-def attribute(dtype_name: str, layers: int, batch: int, prompts: str = "2x1024") -> int:
+def attribute(dtype_name: str, layers: int, batch: int, prompts: str = "2x1024", size: str = "small") -> int:
     """What each family of launches costs INSIDE a step: the step is timed whole and again with the
     family left out (its results are garbage then; only the time is read), and the difference is the
     family's share with all overlap between neighbouring kernels as it is in the real step.  A decode
@@ -324,7 +324,7 @@ def attribute(dtype_name: str, layers: int, batch: int, prompts: str = "2x1024")
     from sandyrt_b200 import core
     from sandyrt_b200.engine.llm import LLM
 
-    raw = load_model_config("small")
+    raw = load_model_config(size)
     from sandyrt_b200.config.gpt2 import GPT2Config
     cfg = GPT2Config.from_dict(raw)
     E, I, V = cfg.n_embd, cfg.inner_dim, cfg.vocab_size
@@ -355,7 +355,7 @@ def attribute(dtype_name: str, layers: int, batch: int, prompts: str = "2x1024")
     return 0
 
 
-def profile_kernels(dtype_name: str, layers: int, batch: int) -> int:
+def profile_kernels(dtype_name: str, layers: int, batch: int, size: str = "small") -> int:
     """Device time per kernel class of one decode step and one 2,048-token prompt step (eager
     launches with a pair of CUDA events around each, so launch gaps are not in the figures)."""
     import numpy as np
@@ -363,7 +363,7 @@ def profile_kernels(dtype_name: str, layers: int, batch: int) -> int:
     from sandyrt_b200 import core
     from sandyrt_b200.engine.step import Engine, StepEntry
 
-    raw = load_model_config("small")
+    raw = load_model_config(size)
     model, cfg = make_model(raw, layers or raw["n_layer"], dtype_name)
     engine = Engine(model, max_tokens=batch * 512 + 4096, max_requests=max(batch, 2), max_step_tokens=4096,
                     use_cuda_graphs=False)
@@ -414,6 +414,7 @@ def main() -> int:
     ap.add_argument("--under-profiler", action="store_true",
                     help="skip the check of the device time against the wall clock (a profiler serialises the launches)")
     ap.add_argument("--attribute", action="store_true", help="print what each family of launches costs inside a step instead")
+    ap.add_argument("--size", default="small", choices=["small", "medium", "xl"], help="model size of --attribute / --profile-kernels")
     ap.add_argument("--attribute-prompts", default="2x1024", help="the prompt step of --attribute: requests x tokens")
     ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
@@ -428,9 +429,9 @@ def main() -> int:
     if args.workload:
         return workload(args.workload, args.dtype, args.layers)
     if args.profile_kernels:
-        return profile_kernels(args.dtype, args.layers, args.batch)
+        return profile_kernels(args.dtype, args.layers, args.batch, args.size)
     if args.attribute:
-        return attribute(args.dtype, args.layers, args.batch, args.attribute_prompts)
+        return attribute(args.dtype, args.layers, args.batch, args.attribute_prompts, args.size)
     if args.warmup < 3:
         args.warmup = 3
 

@@ -51,8 +51,24 @@ layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * ROWS_PER_BLOCK + warp;
     // Gain and offset are weights, which no kernel writes: they are asked for before the wait for
-    // the kernel that produces x, not after the two reductions.
+    // the kernel that produces x, not after the two reductions: into registers for rows up to 1,024 wide,
+    // into shared memory (once for the block's eight rows) beyond.  (Read from global memory where they are
+    // used, a row of 1,600 cost 16 trips to memory, one after the other: 10 us a launch.)
     constexpr bool EARLY = NV <= 8;
+    extern __shared__ __align__(16) uint8_t params_raw[];      // !EARLY && vec: gain [width], offset [width]
+    TW* g_sm = reinterpret_cast<TW*>(params_raw);
+    TW* b_sm = g_sm + width;
+    if (!EARLY && vec) {
+        for (int e = threadIdx.x * 4; e < width; e += ROWS_PER_BLOCK * 32 * 4) {
+            float t4[4];
+            load4(gamma + e, t4);
+            store4(g_sm + e, t4);
+            if (beta) {
+                load4(beta + e, t4);
+                store4(b_sm + e, t4);
+            }
+        }
+    }
     float g[EARLY ? NV : 1][4], b[EARLY ? NV : 1][4];
     if (EARLY && vec && r < n_rows) {
 #pragma unroll
@@ -67,6 +83,7 @@ layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, co
         }
     }
     pdl_wait();
+    if (!EARLY && vec) __syncthreads();      // gain and offset are in shared memory (every warp comes by here)
     if (r >= n_rows) return;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     const TI* xr = x + src * width;
@@ -107,8 +124,8 @@ layernorm_warp_kernel(const TI* __restrict__ x, const TW* __restrict__ gamma, co
 #pragma unroll
                     for (int j = 0; j < 4; j++) { gg[j] = g[i][j]; bb[j] = b[i][j]; }
                 } else {
-                    load4(gamma + e, gg);
-                    if (beta) load4(beta + e, bb);
+                    load4(g_sm + e, gg);
+                    if (beta) load4(b_sm + e, bb);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; j++) y[j] = (v[i][j] - mean) * inv * gg[j] + bb[j];
@@ -167,9 +184,11 @@ int launch(const void* x, const void* gamma, const void* beta, void* out, const 
     auto aligned = [](const void* p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0; };
     const int vec = width % 4 == 0 && aligned(x, 4 * sizeof(TI)) && aligned(gamma, 4 * sizeof(TW)) &&
                     (!beta || aligned(beta, 4 * sizeof(TW))) && aligned(out, 4 * sizeof(TO));
+    // rows wider than 1,024: gain and offset wait in shared memory (at most 2 x 4,096 floats)
 #define WARP_CASE(NV)                                                                                          \
     if (width <= 128 * NV)                                                                                     \
-        return sandy_launch(layernorm_warp_kernel<TI, TW, TO, NV>, grid, block, 0, stream, (const TI*)x,       \
+        return sandy_launch(layernorm_warp_kernel<TI, TW, TO, NV>, grid, block,                                \
+                            (NV > 8 && vec) ? 2 * (size_t)width * sizeof(TW) : 0, stream, (const TI*)x,         \
                             (const TW*)gamma, (const TW*)beta, (TO*)out, rows, n_rows, width, eps, vec)
     WARP_CASE(1); WARP_CASE(2); WARP_CASE(4); WARP_CASE(6); WARP_CASE(8); WARP_CASE(12); WARP_CASE(16);
     WARP_CASE(32);
