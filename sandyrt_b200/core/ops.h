@@ -89,6 +89,9 @@ bool skinny_norm_fusable(const FusedNorm& n, int64_t K, DType out_dtype);
 // inside / norm apart): 1 request .244 / .250, 2: .255 / .262, 4: .267 / .270, 6: .290 / .285, 7: .297 /
 // .288, 8: .303 / .294, 12: .381 / .341, 16: .409 / .361.
 constexpr int kSkinnyNormPaysRows = 4;
+// ... and up to which K: the blocks' norms also grow with the row's width.  One request, ms a decode step, norm
+// inside / apart: GPT-2 small (K 768) .244 / .250, medium (1,024) .572 / .573, xl (1,600) 3.45 / 2.80.
+constexpr int kSkinnyNormPaysK = 1024;
 void gemm_skinny(const Launch& l, const Tensor* a, const FusedNorm* norm, const Tensor& w, const Tensor* bias, Tensor& out,
                  Act act, const Tensor* residual, KVTarget* kv = nullptr);
 constexpr int kSkinnyMaxRows = 64;

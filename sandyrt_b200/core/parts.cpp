@@ -90,7 +90,7 @@ void Linear::run(StepContext& ctx, NormedInput* lazy, const Tensor* a, Tensor& o
     const ops::Launch& l = ctx.launch;
     if (use_tc_ && rows <= ops::kSkinnyMaxRows) {
         ops::FusedNorm fused;
-        const bool fuse = lazy && rows <= ops::kSkinnyNormPaysRows && lazy->fusable(fused) && ops::skinny_norm_fusable(fused, in_, DType::BF16);
+        const bool fuse = lazy && rows <= ops::kSkinnyNormPaysRows && in_ <= ops::kSkinnyNormPaysK && lazy->fusable(fused) && ops::skinny_norm_fusable(fused, in_, DType::BF16);
         if (!fuse && lazy) a = &lazy->tensor();
         if (!fuse && ops::small_gemm_kernel(rows, out_, in_) == ops::SmallGemm::SplitK) {
             ops::gemm_small(l, *a, weight_.view, bias, out, act, residual, kv);
