@@ -374,9 +374,13 @@ void gemm_skinny(const Launch& l, const Tensor* a, const FusedNorm* norm, const 
 constexpr int kSmallMinRows = 17;
 constexpr int kSplitKMinK = 2048;
 constexpr int kSplitKMinCols = 16384;
+// Below 17 rows the streaming kernel keeps the products up to K = 4,096 (8 rows, us alone, streaming / split-K:
+// 768 x 3072 4.7 / 4.7 and a decode step 0.296 / 0.304 ms; 1024 x 4096 5.0 / 5.1; 1280 x 5120 8.1 / 6.2;
+// 1600 x 6400 10.1 / 7.6).
+constexpr int kSplitKMinKFewRows = 5120;
 
 SmallGemm small_gemm_kernel(int64_t M, int64_t N, int64_t K) {
-    if (M < kSmallMinRows) return SmallGemm::Skinny;
+    if (M < kSmallMinRows) return K >= kSplitKMinKFewRows ? SmallGemm::SplitK : SmallGemm::Skinny;
     if (K >= kSplitKMinK || N >= kSplitKMinCols) return SmallGemm::SplitK;
     return SmallGemm::Skinny;
 }

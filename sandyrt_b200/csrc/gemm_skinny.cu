@@ -333,7 +333,12 @@ int launch1(const void* a, const NormArgs& norm, const void* w, const void* bias
             cudaStream_t stream) {
     // 16-byte pieces of one warp's K slice
     const int per_warp = ((K + KCHUNK - 1) / KCHUNK + WARPS - 1) / WARPS;
-    if (per_warp <= 4)
+    // More blocks than SMs: what counts is how many blocks an SM holds, and the short rounds' 80 registers
+    // allow three where the long rounds' 166 to 255 allow one (an 8 x 4800 x 1600 product: 13.7 us with one
+    // round of eight pieces, 7.7 with two rounds of four; GPT-2 xl decode steps of 1 / 8 requests 2.80 / 3.11 ->
+    // 1.89 / 2.23 ms).
+    const bool crowded = MT == 1 && (N + COLS - 1) / COLS > sandy_sm_count();
+    if (per_warp <= 4 || crowded)
         return launch2<MT, FUSE_LN, 4, RV>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
     if (per_warp <= 8 || MT > 1)
         return launch2<MT, FUSE_LN, 8, RV>(a, norm, w, bias, residual, out, M, N, K, lda, ldw, ldr, ldc, act, out_dtype, kv, stream);
