@@ -563,7 +563,7 @@ def test_prefill_attention_far_key(tc):
 
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 32, 33, 64])
 @pytest.mark.parametrize("N,K", [(64, 64), (2304, 768), (777, 240), (50257, 64), (16401, 776), (96, 320), (1000, 96),
-                                 (13, 8)])
+                                 (13, 8), (4800, 1600), (1304, 2056)])     # the last two: more blocks than SMs and a long K
 def test_gemm_skinny(M, N, K):
     """The decode-step product at 1..64 rows, odd N, K that is no multiple of its 32-wide chunks;
     with very many columns, up to 16 rows and nothing fused the kernel whose warps walk the column
