@@ -378,10 +378,15 @@ constexpr int kSplitKMinCols = 16384;
 // 768 x 3072 4.7 / 4.7 and a decode step 0.296 / 0.304 ms; 1024 x 4096 5.0 / 5.1; 1280 x 5120 8.1 / 6.2;
 // 1600 x 6400 10.1 / 7.6).
 constexpr int kSplitKMinKFewRows = 5120;
+constexpr int kSplitKMinKManyRows = 1280;
 
 SmallGemm small_gemm_kernel(int64_t M, int64_t N, int64_t K) {
     if (M < kSmallMinRows) return K >= kSplitKMinKFewRows ? SmallGemm::SplitK : SmallGemm::Skinny;
     if (K >= kSplitKMinK || N >= kSplitKMinCols) return SmallGemm::SplitK;
+    // more than two row tiles of wide rows: the streaming kernel's blocks each fetch all rows (64 x 1,600: 205 KB)
+    // (64 rows, us alone, streaming / split-K: 4800 x 1600 18.7 / 10.4, 1600 x 1600 10.0 / 7.7, 6400 x 1600 20.3 /
+    // 14.5; at 32 rows level; at K = 1,024 the streaming kernel leads: 3072 x 1024 7.2 / 11.9)
+    if (M > 32 && K >= kSplitKMinKManyRows) return SmallGemm::SplitK;
     return SmallGemm::Skinny;
 }
 
