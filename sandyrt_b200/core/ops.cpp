@@ -394,7 +394,7 @@ void gemm_small(const Launch& l, const Tensor& a, const Tensor& w, const Tensor*
                 const Tensor* residual, KVTarget* kv) {
     const int64_t M = a.rows, K = a.cols, N = w.rows;
     if (a.dtype != DType::BF16 || w.dtype != DType::BF16) throw UnsupportedShape("gemm_small takes bfloat16 operands");
-    if (M > kSkinnyMaxRows) throw UnsupportedShape("gemm_small takes at most 64 rows, got " + std::to_string(M));
+    if (M > kSmallMaxRows) throw UnsupportedShape("gemm_small takes at most 256 rows, got " + std::to_string(M));
     if (w.cols != K || out.rows != M || out.cols != N)
         throw KernelError("gemm_small: shapes disagree: a " + dims(a) + ", w " + dims(w) + ", out " + dims(out));
     if (K % 8 || w.ld % 8 || a.ld % 8 || ((uintptr_t)w.data & 15) || ((uintptr_t)a.data & 15))

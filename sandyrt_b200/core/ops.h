@@ -97,6 +97,15 @@ void gemm_skinny(const Launch& l, const Tensor* a, const FusedNorm* norm, const 
 constexpr int kSkinnyMaxRows = 64;
 // tcgen05 with the weight as the wide operand and K split over a cluster, for 17 to 64 rows (gemm_small.cu).
 // small_gemm_kernel: which kernel a bfloat16 product of 17 to 64 rows gets, from its shape alone.
+// The split-K kernel also takes 65 to 256 rows (a short prompt step, or a portion of one): products with a
+// long K and few row tiles, which the tile kernels run on a handful of CTAs (128 x 768 x 3072: six CTAs of 48
+// k-steps each, 18 us inside the step).
+// Prompt steps of one request, us, tile kernels / split-K for the down-projection: 65 tokens 642 / 556, 128: 686 /
+// 595, 129: 680 / 640, 192: 673 / 683, 256: 692 / 697: it pays up to 128 rows (one 128-wide side); the kernel
+// itself takes up to 256.
+constexpr int kSmallMaxRows = 256;
+constexpr int kSmallPaysRows = 128;
+constexpr int kSmallManyRowsMinK = 2048;
 enum class SmallGemm { Skinny, SplitK };
 SmallGemm small_gemm_kernel(int64_t M, int64_t N, int64_t K);
 void gemm_small(const Launch& l, const Tensor& a, const Tensor& w, const Tensor* bias, Tensor& out, Act act,

@@ -100,6 +100,10 @@ void Linear::run(StepContext& ctx, NormedInput* lazy, const Tensor* a, Tensor& o
         return;
     }
     if (lazy) a = &lazy->tensor();
+    if (use_tc_ && rows <= ops::kSmallPaysRows && in_ >= ops::kSmallManyRowsMinK && !kv) {
+        ops::gemm_small(l, *a, weight_.view, bias, out, act, residual, nullptr);
+        return;
+    }
     if (use_tc_) {
         const bool fused_kv = kv && kv->cache.head_dim % 16 == 0 && kv->q_cols % 8 == 0;
         ops::gemm_tc(l, *a, weight_.view, bias, out, act, residual, 0, fused_kv ? kv : nullptr);

@@ -32,15 +32,17 @@
 namespace {
 
 constexpr int NUM_THREADS = 192;
-constexpr int TOKENS = 64;             // the instruction's narrow side: tokens per tile
 constexpr int W_BYTES = BM * BK * 2;   // 128 weight rows x 64 k
-constexpr int A_BYTES = TOKENS * BK * 2;
-constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
-constexpr int PART_BYTES = TOKENS * BM * 4;       // a block's accumulator as floats, [token][column]
 constexpr int MAX_SPLITS = 8;                     // the portable cluster size
+constexpr int MAX_TOKENS = 256;                   // the instruction's narrow side at its widest
 
-template <int STAGES>
+// TOKENS: the instruction's narrow side, tokens per tile: 64 (a decode step), 128 or 256 (a short prompt
+// step, whose products of few row tiles the tile kernels run on a handful of CTAs).
+template <int STAGES, int TOKENS>
 struct Layout {
+    static constexpr int A_BYTES = TOKENS * BK * 2;
+    static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+    static constexpr int PART_BYTES = TOKENS * BM * 4;       // a block's accumulator as floats, [token][column]
     static_assert(STAGES * STAGE_BYTES >= PART_BYTES, "the accumulator is parked in the ring's memory");
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
@@ -149,10 +151,11 @@ __device__ __forceinline__ void finish_dispatch(int m0, int step, int count, int
 }
 
 // grid (splits, tiles), clusters of (splits, 1, 1): blockIdx.x is the block's rank in its cluster.
-template <int STAGES>
+template <int STAGES, int TOKENS>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, EpilogueArgs ep,
                   int M, int N, int K, int steps_per_split, int* __restrict__ status) {
+    constexpr int STAGE_BYTES = Layout<STAGES, TOKENS>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -250,7 +253,8 @@ gemm_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (warp >= 2) {
         if (ep.bias && n < N) bias = __bfloat162float(ep.bias[n]);     // a weight-like input: before the wait
         pdl_wait();              // out, residual and positions may still be in use by kernels before
-        if (ep.kv.k_cache && e < TOKENS) kv_row_target(ep.kv, e, M, kv_page[e], kv_slot[e]);
+        if (ep.kv.k_cache)
+            for (int tok = e; tok < TOKENS; tok += 128) kv_row_target(ep.kv, tok, M, kv_page[tok], kv_slot[tok]);
         epilogue_sync();
         const bool has_work = kt_end > kt_begin;
         const bool ready = has_work ? mbar_wait(accum_bar, 0) : true;
@@ -313,20 +317,20 @@ int choose_splits(int N, int K) {
     return (k_tiles + steps - 1) / steps;
 }
 
-template <int STAGES>
+template <int STAGES, int TOKENS>
 int launch(const CUtensorMap& mw, const CUtensorMap& ma, const EpilogueArgs& ep, int M, int N, int K, int tiles, int splits,
            int steps, int* status, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         const cudaError_t e =
-            cudaFuncSetAttribute(gemm_small_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<STAGES>::TOTAL);
+            cudaFuncSetAttribute(gemm_small_kernel<STAGES, TOKENS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<STAGES, TOKENS>::TOTAL);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(splits, tiles);
     cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = Layout<STAGES>::TOTAL;
+    cfg.dynamicSmemBytes = Layout<STAGES, TOKENS>::TOTAL;
     cfg.stream = stream;
     // (a product that is not split is launched as an ordinary grid, not as clusters of one block)
     cudaLaunchAttribute attr[2];
@@ -345,7 +349,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const EpilogueArgs& ep,
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_small_kernel<STAGES>, mw, ma, ep, M, N, K, steps, status);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_small_kernel<STAGES, TOKENS>, mw, ma, ep, M, N, K, steps, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -356,7 +360,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const EpilogueArgs& ep,
 // and the device's SM count.
 SANDY_API int sandy_gemm_small_splits(int N, int K) { return choose_splits(N, K); }
 
-// a: bfloat16 [M, K] (M <= 64), row stride lda; w: bfloat16 [N, K], row stride ldw; bias: bfloat16 [N] or null;
+// a: bfloat16 [M, K] (M <= 256), row stride lda; w: bfloat16 [N, K], row stride ldw; bias: bfloat16 [N] or null;
 // residual: float [M, N] or null (may be `out`); out: [M, N] bfloat16 (out_dtype 1) or float (0).
 // The key/value arguments as in sandy_gemm_tc.
 // status: bits 0-2 a barrier wait ran out, bit 3 a key/value write had no page behind it.
@@ -367,7 +371,8 @@ SANDY_API int sandy_gemm_small(const void* a, const void* w, const void* bias, c
                                int page_size, int num_pages, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return SANDY_OK;
     if (!a || !w || !out || K <= 0) return SANDY_ERR_ARGUMENT;
-    if (M > TOKENS || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return SANDY_ERR_UNSUPPORTED;
+    if (M > MAX_TOKENS || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return SANDY_ERR_UNSUPPORTED;
+    const int tokens = M <= 64 ? 64 : (M <= 128 ? 128 : 256);
     if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return SANDY_ERR_UNSUPPORTED;
     if (out_dtype != SANDY_F32 && out_dtype != SANDY_BF16) return SANDY_ERR_UNSUPPORTED;
     const int tiles = (N + BM - 1) / BM, k_tiles = (K + BK - 1) / BK;
@@ -375,7 +380,7 @@ SANDY_API int sandy_gemm_small(const void* a, const void* w, const void* bias, c
     const int splits = choose_splits(N, K);
     CUtensorMap mw, ma;
     if (!get_map(w, N, K, ldw, BM, &mw)) return SANDY_ERR_UNSUPPORTED;
-    if (!get_map(a, M, K, lda, TOKENS, &ma)) return SANDY_ERR_UNSUPPORTED;
+    if (!get_map(a, M, K, lda, tokens, &ma)) return SANDY_ERR_UNSUPPORTED;
     KVWrite kv{(bf16*)k_cache, (bf16*)v_cache, page_stride, block_table, token_seq, positions,
                max_blocks, q_cols, kv_cols, head_dim, page_size, num_pages};
     if (k_cache) {
@@ -387,6 +392,8 @@ SANDY_API int sandy_gemm_small(const void* a, const void* w, const void* bias, c
     const int steps = (k_tiles + splits - 1) / splits;
     // many tiles and no split (a vocabulary projection): three stages, so that three blocks share an SM and
     // the tiles run as one wave; else a deeper ring for the one block an SM gets
-    if (splits == 1) return launch<3>(mw, ma, ep, M, N, K, tiles, splits, steps, status, stream);
-    return launch<6>(mw, ma, ep, M, N, K, tiles, splits, steps, status, stream);
+    if (tokens == 128) return launch<6, 128>(mw, ma, ep, M, N, K, tiles, splits, steps, status, stream);
+    if (tokens == 256) return launch<4, 256>(mw, ma, ep, M, N, K, tiles, splits, steps, status, stream);
+    if (splits == 1) return launch<3, 64>(mw, ma, ep, M, N, K, tiles, splits, steps, status, stream);
+    return launch<6, 64>(mw, ma, ep, M, N, K, tiles, splits, steps, status, stream);
 }

@@ -537,7 +537,7 @@ def gemm_skinny(a, w, bias, out, *, act=None, residual=None, norm=None, kv=None)
 
 
 def gemm_small(a, w, bias, out, *, act=None, residual=None, kv=None) -> None:
-    """out = act(a @ w.T + bias) + residual for up to 64 rows on the tcgen05 tensor cores with the
+    """out = act(a @ w.T + bias) + residual for up to 256 rows on the tcgen05 tensor cores with the
     weight as the instruction's wide operand and K split over a cluster's blocks (gemm_small.cu).
     Same operand rules as gemm_tc; `kv` as in gemm_skinny."""
     M, K = a.shape
@@ -545,8 +545,8 @@ def gemm_small(a, w, bias, out, *, act=None, residual=None, kv=None) -> None:
     _cuda(a, w, bias, out, residual)
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise UnsupportedShape("gemm_small takes bfloat16 operands")
-    if M > 64:
-        raise UnsupportedShape(f"gemm_small takes at most 64 rows, got {M}")
+    if M > 256:
+        raise UnsupportedShape(f"gemm_small takes at most 256 rows, got {M}")
     if w.shape[1] != K or tuple(out.shape) != (M, N):
         raise KernelError(f"gemm_small: shapes disagree: a {(M, K)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:

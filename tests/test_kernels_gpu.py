@@ -659,7 +659,7 @@ def test_gemm_skinny_writes_keys_and_values_into_the_pages(H, Hkv, D, seqs):
     assert torch.equal(arena_a, arena_b) and float(arena_a.abs().sum()) > 0
 
 
-@pytest.mark.parametrize("M", [1, 17, 24, 32, 33, 47, 64])
+@pytest.mark.parametrize("M", [1, 17, 24, 32, 33, 47, 64, 65, 128, 200, 256])
 @pytest.mark.parametrize("N,K", [(64, 64), (2304, 768), (768, 3072), (777, 240), (50257, 64), (16401, 776), (96, 320),
                                  (1000, 96), (13, 8), (136, 1600), (520, 4104)])
 def test_gemm_small(M, N, K):
