@@ -291,6 +291,9 @@ Json call_global(const std::string& m, const Json& a) {
     }
     if (m == "decode_splits")
         return Json(ops::decode_splits((int)a.at("n_tokens").as_int(), (int)a.at("n_heads").as_int(), (int)a.at("max_kv").as_int(), (int)geti(a, "sms", 0)));
+    if (m == "small_gemm_kernel")                     // {"M", "N", "K"} -> "split_k" | "streaming": the rule for products of up to 64 rows
+        return Json(ops::small_gemm_kernel(a.at("M").as_int(), a.at("N").as_int(), a.at("K").as_int()) == ops::SmallGemm::SplitK
+                        ? std::string("split_k") : std::string("streaming"));
     if (m == "leave_out") {                           // {"families": [...]}: launches to skip (timing only); [] restores
         std::vector<std::string> families;
         if (a.has("families"))

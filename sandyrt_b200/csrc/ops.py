@@ -216,8 +216,8 @@ _DECODE_HEAD_DIMS = {torch.bfloat16: (16, 32, 64, 128, 256), torch.float32: (16,
 
 def decode_splits(n_tokens: int, n_heads: int, max_kv: int, sms: Optional[int] = None) -> int:
     """How many blocks share the keys of one (token, head) pair in a decode step (the host library's
-    rule, core/ops.cpp): enough to fill the GPU's SMs a few times over, but no block with fewer than
-    64 keys, and never a cluster of 6 or 7 blocks."""
+    rule, core/ops.cpp): about four blocks an SM in all, more where a block would walk more than some 256
+    keys alone (up to eight an SM), no block with fewer than 64 keys, and never a cluster of 6 or 7 blocks."""
     from .. import core
 
     return core.call("global", None, "decode_splits", n_tokens=n_tokens, n_heads=n_heads, max_kv=max_kv, sms=sms or 0)
@@ -580,6 +580,14 @@ def gemm_small(a, w, bias, out, *, act=None, residual=None, kv=None) -> None:
         ctypes.c_int(head_dim), ctypes.c_int(page_size), ctypes.c_int(num_pages), _p(kernel_status(w.device)),
         _stream())
     _check(code, f"gemm_small(M={M},N={N},K={K},kv={kv is not None})")
+
+
+def small_gemm_kernel(M: int, N: int, K: int) -> str:
+    """Which kernel the engine gives a bfloat16 product of up to 64 rows: "streaming" (gemm_skinny) or
+    "split_k" (gemm_small).  A rule of the shape alone (host library, no GPU needed)."""
+    from .. import core
+
+    return core.call("global", None, "small_gemm_kernel", M=M, N=N, K=K)
 
 
 def gemm_small_splits(N: int, K: int) -> int:

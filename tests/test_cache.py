@@ -160,3 +160,30 @@ def test_decode_splits_avoid_clusters_of_six_and_seven():
                 assert n <= max(1, max_kv // 64) or n == 5
                 seen.add(n)
     assert {1, 2, 3, 4, 5, 8} <= seen
+
+
+def test_decode_splits_at_the_measured_points():
+    """The rule's answers where whole decode steps were measured (12 heads of 64, 148 SMs): about four blocks
+    an SM, to the nearest; more for long ranges, up to eight blocks an SM."""
+    from sandyrt_b200.csrc.ops import decode_splits
+
+    at = lambda tokens, ctx, heads=12: decode_splits(tokens, heads, ctx, sms=148)
+    assert [at(b, 400) for b in (8, 12, 16, 24, 32, 48, 64)] == [5, 4, 3, 2, 2, 2, 1]
+    assert at(32, 965) == 3 and at(8, 965) == 5
+    assert at(32, 1024, heads=16) == 2          # GPT-2 medium's mixed workload
+    assert at(64, 600, heads=25) == 1           # GPT-2 xl, 64 requests: one block a pair
+
+
+def test_small_product_rule():
+    """Which kernel takes a product of up to 64 rows is a rule of its shape (the kernels add in different
+    orders, so it must not depend on a timing)."""
+    from sandyrt_b200.csrc.ops import small_gemm_kernel
+
+    # GPT-2 small's four products and the vocabulary
+    assert [small_gemm_kernel(8, n, k) for n, k in ((2304, 768), (768, 768), (3072, 768), (768, 3072), (50257, 768))] == ["streaming"] * 5
+    assert [small_gemm_kernel(64, n, k) for n, k in ((2304, 768), (768, 768), (3072, 768))] == ["streaming"] * 3
+    assert small_gemm_kernel(17, 768, 3072) == "split_k" and small_gemm_kernel(64, 50257, 768) == "split_k"
+    # wide models: a long K below 17 rows, any K from 1,280 above 32 rows
+    assert small_gemm_kernel(8, 1600, 6400) == "split_k" and small_gemm_kernel(8, 1024, 4096) == "streaming"
+    assert small_gemm_kernel(64, 4800, 1600) == "split_k" and small_gemm_kernel(32, 4800, 1600) == "streaming"
+    assert small_gemm_kernel(64, 3072, 1024) == "streaming"
