@@ -410,9 +410,25 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
             const int k = (c_begin + u) * KCHUNK + t * 8;
             wn[h][u] = (n_ok[h] && c_begin + u < c_end && k < K) ? ldg16_stream(wrow[h] + k) : zero;
         }
-    // thread i writes outputs i, i + 256, ...: always column i % 16 of the block
+    // thread i writes outputs i, i + 256, ...: always column i % 16 of the block, rows i / 16 + 16 j
     const int my_col = n0 + (int)(threadIdx.x % COLS2);
     const float my_bias = (bias && my_col < N) ? __bfloat162float(bias[my_col]) : 0.0f;
+    // The pages its key/value elements go to: two dependent loads a row, asked for now (the index arrays are
+    // the step's input, complete by now) and not in the write-back, where they were MT pairs of trips to
+    // memory one after the other (ncu: the q/k/v product of 64 rows 14.2 us against 11.2 for the wider
+    // up-projection).
+    int kv_pos[MT], kv_page[MT];
+#pragma unroll
+    for (int j = 0; j < MT; j++) {
+        kv_pos[j] = 0;
+        kv_page[j] = -1;
+        const int m = (int)(threadIdx.x / COLS2) + 16 * j;
+        if (kv.k_cache && m < M && my_col >= kv.q_cols && my_col < N) {
+            kv_pos[j] = kv.positions[m];
+            const int b = kv_pos[j] / kv.page_size;
+            kv_page[j] = (kv_pos[j] >= 0 && b < kv.max_blocks) ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
+        }
+    }
 
     pdl_launch_dependents();
     pdl_wait();
@@ -455,8 +471,9 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
             partial[warp][mt * 16 + g + 8][8 * h + 2 * t + 1] = acc[mt][h][3];
         }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < MT * 16 * COLS2; idx += WARPS * 32) {
-        const int m = idx / COLS2, j = idx % COLS2;
+#pragma unroll
+    for (int it = 0; it < MT; it++) {
+        const int m = (int)(threadIdx.x / COLS2) + 16 * it, j = (int)(threadIdx.x % COLS2);
         const int col = n0 + j;
         if (m >= M || col >= N) continue;
         float v = partial[0][m][j];
@@ -472,9 +489,7 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
             const bool is_v = c >= kv.kv_cols;
             const int c2 = is_v ? c - kv.kv_cols : c;
             const int head = c2 / kv.head_dim, d = c2 % kv.head_dim;
-            const int pos = kv.positions[m];
-            const int b = pos / kv.page_size;
-            const int page = (pos >= 0 && b < kv.max_blocks) ? kv.block_table[(size_t)kv.token_seq[m] * kv.max_blocks + b] : -1;
+            const int pos = kv_pos[it], page = kv_page[it];
             if (page < 0 || page >= kv.num_pages) {
                 if (kv.status) atomicOr(kv.status, 8);
             } else {
