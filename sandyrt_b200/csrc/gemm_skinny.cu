@@ -15,6 +15,10 @@
 // warp-level tensor-core instruction (mma.sync m16n8k16: 16 tokens x 8 columns), which is far
 // more than this bandwidth-bound product needs.
 //
+// Three forms live in this file: the one described here (8 columns a block; every product of up to 16
+// rows, and the narrow products beyond), one with 16 columns a block for 17 to 64 rows and 1,536 columns
+// and more, and one whose warps walk the column groups of a vocabulary projection (both further down).
+//
 // Each lane reads the weight in 16-byte pieces straight from global memory.  The 8
 // consecutive k of a piece are fed to two consecutive mma steps; since a dot product does not
 // care in which order its terms are paired, the same assignment of k to fragment slots is
